@@ -1,0 +1,184 @@
+/*
+ * qmlb200 -- C ABI of the B200 (sm_100a) kernels for the qml-lightning
+ * inference/training hot path: FCHL19 representation (forward, vector-Jacobian
+ * product, explicit Jacobian), per-element PCA projection, SORF / RFF feature
+ * maps with the per-molecule sum, the dot with the regression weights and the
+ * force back-propagation, and the normal-equation accumulation.
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer unless its comment says "host";
+ *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *    nothing here synchronises the device or allocates device memory;
+ *  - every function returns QMLB_OK (0) or an error code; qmlb_last_error()
+ *    returns a thread-local message for the last non-zero return;
+ *  - tensors are dense row-major with the shapes given in the comments;
+ *  - `X  f32[nb, A, 3]` coordinates, `Z f32[nb, A]` nuclear charges (0 = padding),
+ *    `atom_counts i32[nb]`: the tensor contract of the upstream project
+ *    (README.md:69-75); atoms a >= atom_counts[m] of molecule m are padding;
+ *  - `cell` / `inv_cell` f32[nb,3,3] or NULL for non-periodic input
+ *    (upstream passes an empty [0,3,3] tensor).
+ *
+ * Each declaration names the upstream interface it replaces (paths inside the
+ * upstream qml-lightning tree).
+ */
+#ifndef QMLB200_H
+#define QMLB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QMLB_OK 0
+#define QMLB_ERR_INVALID 1     /* bad argument (null pointer, size, unsupported shape) */
+#define QMLB_ERR_CUDA 2        /* a CUDA runtime call or launch failed */
+#define QMLB_ERR_UNSUPPORTED 3 /* valid request outside the implemented range */
+
+typedef void *qmlb_stream_t;
+
+/* FCHL19 hyper-parameters at kernel level.  `three_body_weight` is the value
+ * AFTER the constructor scaling sqrt(eta3/pi)*w (representations/FCHL.py:35);
+ * Rs2/Rs3 are the radial grids of FCHL.py:39-40. */
+typedef struct qmlb_fchl_params {
+    const float *species; /* f32[nspecies] charges defining the element index */
+    int nspecies;
+    const float *Rs2;     /* f32[nRs2] */
+    int nRs2;
+    const float *Rs3;     /* f32[nRs3] */
+    int nRs3;
+    float eta2, eta3, two_body_decay, three_body_weight, three_body_decay, rcut;
+} qmlb_fchl_params;
+
+const char *qmlb_last_error(void);
+int qmlb_version(void);
+
+/* repsize = nspecies*nRs2 + nspecies*(nspecies+1)*nRs3  (FCHL.py:42) */
+int qmlb_fchl19_repsize(int nspecies, int nRs2, int nRs3);
+
+/* ---- element typing and neighbour lists ------------------------------------------------- */
+
+/* get_element_types_kernel / getElementTypesCUDA (cuda/fchl_cuda_kernel.cu:1716-1757),
+ * op qml_lightning_fchl::get_element_types (cuda/torchscript/FCHL19.cpp:38-64).
+ * out i32[nb, A]: index of Z in species, -1 when absent; padded atoms get 0 as upstream's zero-init. */
+int qmlb_element_types(const float *Z, const int *atom_counts, const float *species, int nspecies, int nb, int A,
+                       int *element_types, qmlb_stream_t stream);
+
+/* get_num_neighbours_kernel / getNumNeighboursCUDA (cuda/pairlist_kernel.cu:145-224, 462-480),
+ * op qml_lightning_fchl::get_num_neighbours (FCHL19.cpp:66-86).
+ * out i32[nb, A_out] (A_out = max(atom_counts) upstream; columns >= atom_counts[m] are zero). */
+int qmlb_num_neighbours(const float *X, const int *atom_counts, int nb, int A, float rcut, const float *cell,
+                        const float *inv_cell, int *num_neighbours, int A_out, qmlb_stream_t stream);
+
+/* get_neighbour_list_kernel / getNeighbourListCUDA (cuda/pairlist_kernel.cu:326-391, 508-526),
+ * op qml_lightning_fchl::get_neighbour_list (FCHL19.cpp:88-112).
+ * out i32[nb, A_out, max_neighbours]: ascending j, padded with -1 (filled here). */
+int qmlb_neighbour_list(const float *X, const int *atom_counts, int nb, int A, float rcut, const float *cell,
+                        const float *inv_cell, int max_neighbours, int *neighbour_list, int A_out,
+                        qmlb_stream_t stream);
+
+/* ---- FCHL19 ----------------------------------------------------------------------------- */
+
+/* fchl19_representation_cuda / FCHLCuda (cuda/fchl_cuda_kernel.cu:476-674, 1804-1846),
+ * get_fchl_representation (cuda/fchl_cuda.cpp:56-90, torchscript/FCHL19.cpp:114-150), the forward of op
+ * qml_lightning_fchl::fchl_forwards (FCHL19.cpp:244-277).  Neighbours are found inside the kernel
+ * (rule 0 < r^2 < rcut^2, pairlist_kernel.cu:386), so no neighbour list is passed.
+ * rep f32[*, repsize]: row of atom (m,a) is  row_of_slot[m*A+a]  when row_of_slot != NULL (rows < 0 are
+ * skipped), else m*A+a; in the latter case padded atoms are written as zero rows. */
+int qmlb_fchl19_forward(const float *X, const float *Z, const int *atom_counts, int nb, int A,
+                        const qmlb_fchl_params *p, const float *cell, const float *inv_cell,
+                        const int *row_of_slot, float *rep, qmlb_stream_t stream);
+
+/* fchl19_backwards_cuda / FCHLBackwardsCuda (cuda/fchl_cuda_kernel.cu:1325-1714, 1885-1926),
+ * fchl_backwards (fchl_cuda.cpp:119-155, FCHL19.cpp:210-239), the backward of fchl_forwards (FCHL19.cpp:279-315):
+ * grad_X[m,a,:] = sum_i sum_c grad_rep[row(m,i), c] * d rep[m,i,c] / d r_a.
+ * grad_X f32[nb, A, 3] is fully overwritten (padded atoms get zeros).
+ * atom_energy (optional, f32 per row) is summed per molecule into mol_energy f32[nb] when both are non-NULL. */
+int qmlb_fchl19_backward(const float *X, const float *Z, const int *atom_counts, int nb, int A,
+                         const qmlb_fchl_params *p, const float *cell, const float *inv_cell,
+                         const int *row_of_slot, const float *grad_rep, float *grad_X, const float *atom_energy,
+                         float *mol_energy, qmlb_stream_t stream);
+
+/* fchl19_representation_and_derivative_cuda / FCHLRepresentationAndDerivativeCuda
+ * (cuda/fchl_cuda_kernel.cu:676-1005, 1928-1964), get_fchl_and_derivative (fchl_cuda.cpp:157-202,
+ * FCHL19.cpp:152-208).  rep f32[nb,A,repsize]; jac f32[nb,A,A,3,repsize] with
+ * jac[m,i,a,x,c] = d rep[m,i,c] / d r_{a,x}.  Both are fully overwritten. */
+int qmlb_fchl19_forward_jacobian(const float *X, const float *Z, const int *atom_counts, int nb, int A,
+                                 const qmlb_fchl_params *p, const float *cell, const float *inv_cell, float *rep,
+                                 float *jac, qmlb_stream_t stream);
+
+/* ---- element grouping (replaces the boolean-mask gathers and torch.where host syncs of
+ *      models/hadamard_features.py:99-107 and models/kernel.py:141-150) -------------------- */
+
+/* Rows of the per-atom work arrays are ordered by model element, each element group padded to a multiple of
+ * QMLB_ROW_TILE rows.  Given Z and the model's `elements` (f32[nelements] charges) this writes
+ *   row_of_slot i32[nb*A]        row of atom (m,a) or -1 (padding / element not in `elements`)
+ *   slot_of_row i32[rows_cap]    m*A+a of a row, -1 for padding rows
+ *   group_start i32[nelements+1] first row of each element group (group_start[nelements] = rows in use)
+ * Within a group rows follow (m,a) order, so the result is deterministic.
+ * rows_cap must be >= qmlb_rows_capacity(n_atoms_upper, nelements).  `scratch` is
+ * qmlb_group_scratch_bytes(nb, nelements) bytes of device memory. */
+#define QMLB_ROW_TILE 64
+size_t qmlb_rows_capacity(size_t n_atoms_upper, int nelements);
+size_t qmlb_group_scratch_bytes(int nb, int nelements);
+int qmlb_group_by_element(const float *Z, const int *atom_counts, const float *elements, int nelements, int nb,
+                          int A, int *row_of_slot, int *slot_of_row, int *group_start, size_t rows_cap,
+                          void *scratch, qmlb_stream_t stream);
+
+/* ---- PCA projection ----------------------------------------------------------------------- */
+
+/* project_representation = torch.matmul(X, reductor) per element (representations/dimensionality_reduction.py:47-58;
+ * call sites models/hadamard_features.py:111, models/random_features.py:96, models/kernel.py:154).
+ * in f32[rows_cap, K], reductors f32[nelements, K, N], out f32[rows_cap, N]; rows are element-grouped as above.
+ * transpose = 0: out = in . P_e            (K = repsize, N = npcas)
+ * transpose = 1: out = in . P_e^T          (the autograd backward: in is [rows, npcas], out [rows, repsize]) */
+int qmlb_pca_project(const float *in, const float *reductors, const int *group_start, int nelements, size_t rows_cap,
+                     int repsize, int npcas, int transpose, float *out, qmlb_stream_t stream);
+
+/* ---- SORF ----------------------------------------------------------------------------------- */
+
+/* hadamard_kernel / hadamard_gpu (cuda/hadamard_kernel.cu:5-102, 719-737), hadamard_transform_gpu
+ * (torchscript/SORF.cpp:24-36), forward of op qml_lightning_sorf::get_SORF_coefficients (SORF.cpp:76-87).
+ * u f32[n,N], D f32[T,S,N] (+-1), out f32[n,S,N] = normalisation * N^(-T/2) * (H D_{T-1} ... H D_0) u. */
+int qmlb_sorf_coefficients(const float *u, const float *D, int n, int N, int S, int T, float normalisation,
+                           float *out, qmlb_stream_t stream);
+
+/* hadamard_kernel_backwards / hadamard_backwards_gpu (hadamard_kernel.cu:204-312, 758-776), backward of
+ * get_SORF_coefficients (SORF.cpp:89-101).  grad f32[n,S,N] -> out f32[n,N]. */
+int qmlb_sorf_coefficients_backward(const float *grad, const float *D, int n, int N, int S, int T,
+                                    float normalisation, float *out, qmlb_stream_t stream);
+
+/* compute_cos_features_kernel / cos_features_gpu (hadamard_kernel.cu:778-814), CosFeaturesCUDA (SORF.cpp:52-61),
+ * forward of op qml_lightning_sorf::get_cos_features (SORF.cpp:106-119).
+ * coeffs f32[n,F], bias f32[F], batch_indexes i32[n] (molecule of each row, non-decreasing or arbitrary),
+ * out f32[nmol,F] = sum over rows of sqrt(2/F) cos(coeffs + bias); fully overwritten. */
+int qmlb_cos_features(const float *coeffs, const float *bias, const int *batch_indexes, int n, int F, int nmol,
+                      float *out, qmlb_stream_t stream);
+
+/* compute_cos_derivative_features_kernel / cos_derivative_features_gpu (hadamard_kernel.cu:816-854),
+ * backward of get_cos_features (SORF.cpp:121-133): out[a,f] = grads[mol(a),f] * -sin(coeffs+bias) * sqrt(2/F). */
+int qmlb_cos_features_backward(const float *grads, const float *coeffs, const float *bias, const int *batch_indexes,
+                               int n, int F, float *out, qmlb_stream_t stream);
+
+/* Packed SORF parameters for the fused kernel below: sign diagonals, bias and pre-scaled weights re-ordered to
+ * the register layout of the in-register/shared-memory FWHT.  Source tensors are the model attributes
+ * Dmat f32[nelements,T,S,N], bias f32[nelements,S*N], alpha f32[S*N] (models/hadamard_features.py:34-41,119-121).
+ * `packed` is qmlb_sorf_pack_bytes(...) bytes of device memory, written by qmlb_sorf_pack. */
+size_t qmlb_sorf_pack_bytes(int nelements, int N, int S, int T);
+int qmlb_sorf_pack(const float *Dmat, const float *bias, const float *alpha, int nelements, int N, int S, int T,
+                   void *packed, qmlb_stream_t stream);
+
+/* Fused replacement of the chain get_SORF_coefficients -> get_cos_features -> matmul(Ztest, alpha) and of its
+ * autograd backward (models/hadamard_features.py:113-121; SORF.cpp:89-101,121-133): per row a
+ *   atom_energy[a] = sum_f alpha_f sqrt(2/F) cos(c_af + b_f),   c = (sqrt(N)/sigma) N^(-T/2) (H D)^T x_a
+ *   grad_x[a,:]    = d atom_energy[a] / d x_a
+ * without materialising c.  x f32[rows_cap,N] element-grouped; fast_math != 0 uses the SFU sin/cos. */
+int qmlb_sorf_energy_grad(const float *x, const int *group_start, const int *slot_of_row, int nelements,
+                          size_t rows_cap, int N, int S, int T, float sigma, const void *packed, int fast_math,
+                          float *atom_energy, float *grad_x, qmlb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QMLB200_H */

@@ -1,0 +1,269 @@
+"""Thin torch-tensor wrappers over the C ABI of ``libqmlb200.so``.
+
+PyTorch is used only as the owner of device memory and of the current CUDA stream: every function checks its tensors
+(CUDA, contiguous, dtype), allocates outputs with ``torch.empty`` and passes raw pointers plus the current stream to
+the C entry point of the same name (``qmlb_<name>``).  No arithmetic happens in Python.
+"""
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+from ._lib import FchlParamsC, check
+
+ROW_TILE = 64  # QMLB_ROW_TILE
+
+
+def _stream(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _p(t, dtype=None, name='tensor'):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")  # wording of the upstream TORCH_CHECKs (FCHL19.cpp:40-44)
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError(f"{name} must have dtype {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _cells(cell, inv_cell):
+    """Upstream passes empty [0,3,3] tensors for non-periodic input; the C ABI takes NULL."""
+    if cell is None or cell.numel() == 0:
+        return None, None
+    return cell.contiguous().float(), inv_cell.contiguous().float()
+
+
+class FchlKernelParams:
+    """Device-resident FCHL19 grids plus the kernel-level scalars (``qmlb_fchl_params``)."""
+
+    def __init__(self, species, Rs2, Rs3, eta2, eta3, two_body_decay, three_body_weight, three_body_decay, rcut):
+        self.species = species.contiguous().float()
+        self.Rs2 = Rs2.contiguous().float()
+        self.Rs3 = Rs3.contiguous().float()
+        self.scalars = tuple(float(v) for v in (eta2, eta3, two_body_decay, three_body_weight, three_body_decay, rcut))
+        self.repsize = _lib.load().qmlb_fchl19_repsize(self.species.numel(), self.Rs2.numel(), self.Rs3.numel())
+
+    def c(self):
+        eta2, eta3, d2, w3, d3, rcut = self.scalars
+        return FchlParamsC(_p(self.species, torch.float32, 'species'), self.species.numel(),
+                           _p(self.Rs2, torch.float32, 'Rs2'), self.Rs2.numel(),
+                           _p(self.Rs3, torch.float32, 'Rs3'), self.Rs3.numel(), eta2, eta3, d2, w3, d3, rcut)
+
+
+def _batch(X, Z, atom_counts):
+    if X.dim() == 2:
+        X = X.unsqueeze(0)
+    if Z.dim() == 1:
+        Z = Z.unsqueeze(0)
+    X = X.contiguous()
+    Z = Z.contiguous()
+    nb, A = Z.shape
+    return X, Z, atom_counts.contiguous(), nb, A
+
+
+def element_types(X, Z, atom_counts, species):
+    X, Z, atom_counts, nb, A = _batch(X, Z, atom_counts)
+    out = torch.zeros(nb, A, dtype=torch.int32, device=Z.device)
+    check(_lib.load().qmlb_element_types(_p(Z, torch.float32, 'charges'), _p(atom_counts, torch.int32, 'natom_counts'),
+                                         _p(species, torch.float32, 'species'), species.numel(), nb, A, _p(out),
+                                         _stream(Z.device)), 'qmlb_element_types')
+    return out
+
+
+def num_neighbours(X, atom_counts, rcut, cell=None, inv_cell=None, A_out=None):
+    if X.dim() == 2:
+        X = X.unsqueeze(0)
+    X = X.contiguous()
+    nb, A = X.shape[0], X.shape[1]
+    A_out = A if A_out is None else int(A_out)
+    cell, inv_cell = _cells(cell, inv_cell)
+    out = torch.zeros(nb, A_out, dtype=torch.int32, device=X.device)
+    check(_lib.load().qmlb_num_neighbours(_p(X, torch.float32, 'coordinates'), _p(atom_counts.contiguous(), torch.int32, 'natoms'),
+                                          nb, A, float(rcut), _p(cell), _p(inv_cell), _p(out), A_out, _stream(X.device)),
+          'qmlb_num_neighbours')
+    return out
+
+
+def neighbour_list(X, atom_counts, max_neighbours, rcut, cell=None, inv_cell=None, A_out=None):
+    if X.dim() == 2:
+        X = X.unsqueeze(0)
+    X = X.contiguous()
+    nb, A = X.shape[0], X.shape[1]
+    A_out = A if A_out is None else int(A_out)
+    cell, inv_cell = _cells(cell, inv_cell)
+    out = torch.full((nb, A_out, int(max_neighbours)), -1, dtype=torch.int32, device=X.device)
+    check(_lib.load().qmlb_neighbour_list(_p(X, torch.float32, 'coordinates'), _p(atom_counts.contiguous(), torch.int32, 'natoms'),
+                                          nb, A, float(rcut), _p(cell), _p(inv_cell), int(max_neighbours), _p(out), A_out,
+                                          _stream(X.device)), 'qmlb_neighbour_list')
+    return out
+
+
+def fchl19_forward(X, Z, atom_counts, params, cell=None, inv_cell=None, row_of_slot=None, out=None):
+    X, Z, atom_counts, nb, A = _batch(X, Z, atom_counts)
+    cell, inv_cell = _cells(cell, inv_cell)
+    if out is None:
+        assert row_of_slot is None
+        out = torch.empty(nb, A, params.repsize, dtype=torch.float32, device=X.device)
+    pc = params.c()
+    check(_lib.load().qmlb_fchl19_forward(_p(X, torch.float32, 'coordinates'), _p(Z, torch.float32, 'charges'),
+                                          _p(atom_counts, torch.int32, 'atom_counts'), nb, A, ctypes.byref(pc), _p(cell),
+                                          _p(inv_cell), _p(row_of_slot, torch.int32, 'row_of_slot'),
+                                          _p(out, torch.float32, 'rep'), _stream(X.device)), 'qmlb_fchl19_forward')
+    return out
+
+
+def fchl19_backward(X, Z, atom_counts, params, grad_rep, cell=None, inv_cell=None, row_of_slot=None, atom_energy=None):
+    X, Z, atom_counts, nb, A = _batch(X, Z, atom_counts)
+    cell, inv_cell = _cells(cell, inv_cell)
+    grad_X = torch.empty(nb, A, 3, dtype=torch.float32, device=X.device)
+    mol_energy = torch.empty(nb, dtype=torch.float32, device=X.device) if atom_energy is not None else None
+    pc = params.c()
+    check(_lib.load().qmlb_fchl19_backward(_p(X, torch.float32, 'coordinates'), _p(Z, torch.float32, 'charges'),
+                                           _p(atom_counts, torch.int32, 'atom_counts'), nb, A, ctypes.byref(pc), _p(cell),
+                                           _p(inv_cell), _p(row_of_slot, torch.int32, 'row_of_slot'),
+                                           _p(grad_rep.contiguous(), torch.float32, 'grad_rep'), _p(grad_X),
+                                           _p(atom_energy, torch.float32, 'atom_energy'), _p(mol_energy),
+                                           _stream(X.device)), 'qmlb_fchl19_backward')
+    return (grad_X, mol_energy) if atom_energy is not None else grad_X
+
+
+def fchl19_forward_jacobian(X, Z, atom_counts, params, cell=None, inv_cell=None):
+    X, Z, atom_counts, nb, A = _batch(X, Z, atom_counts)
+    cell, inv_cell = _cells(cell, inv_cell)
+    rep = torch.empty(nb, A, params.repsize, dtype=torch.float32, device=X.device)
+    jac = torch.empty(nb, A, A, 3, params.repsize, dtype=torch.float32, device=X.device)
+    pc = params.c()
+    check(_lib.load().qmlb_fchl19_forward_jacobian(_p(X, torch.float32, 'coordinates'), _p(Z, torch.float32, 'charges'),
+                                                   _p(atom_counts, torch.int32, 'atom_counts'), nb, A, ctypes.byref(pc),
+                                                   _p(cell), _p(inv_cell), _p(rep), _p(jac), _stream(X.device)),
+          'qmlb_fchl19_forward_jacobian')
+    return rep, jac
+
+
+class Grouping:
+    """Element-grouped row order of one batch (see ``qmlb_group_by_element``)."""
+
+    def __init__(self, row_of_slot, slot_of_row, group_start, rows_cap, nelements):
+        self.row_of_slot, self.slot_of_row, self.group_start = row_of_slot, slot_of_row, group_start
+        self.rows_cap, self.nelements = rows_cap, nelements
+
+
+def group_by_element(Z, atom_counts, elements, n_atoms_upper=None):
+    Z = Z.contiguous()
+    nb, A = Z.shape
+    lib = _lib.load()
+    nel = elements.numel()
+    upper = nb * A if n_atoms_upper is None else min(int(n_atoms_upper), nb * A)
+    rows_cap = lib.qmlb_rows_capacity(upper, nel)
+    dev = Z.device
+    row_of_slot = torch.empty(nb * A, dtype=torch.int32, device=dev)
+    slot_of_row = torch.empty(rows_cap, dtype=torch.int32, device=dev)
+    group_start = torch.empty(nel + 1, dtype=torch.int32, device=dev)
+    scratch = torch.empty(lib.qmlb_group_scratch_bytes(nb, nel), dtype=torch.uint8, device=dev)
+    check(lib.qmlb_group_by_element(_p(Z, torch.float32, 'charges'), _p(atom_counts.contiguous(), torch.int32, 'atom_counts'),
+                                    _p(elements.contiguous(), torch.float32, 'elements'), nel, nb, A, _p(row_of_slot),
+                                    _p(slot_of_row), _p(group_start), rows_cap, _p(scratch), _stream(dev)),
+          'qmlb_group_by_element')
+    return Grouping(row_of_slot, slot_of_row, group_start, rows_cap, nel)
+
+
+def pca_project(inp, reductors, grouping, transpose=False, out=None):
+    nel, repsize, npcas = reductors.shape
+    rows = grouping.rows_cap
+    width = repsize if transpose else npcas
+    if out is None:
+        out = torch.empty(rows, width, dtype=torch.float32, device=inp.device)
+    check(_lib.load().qmlb_pca_project(_p(inp, torch.float32, 'in'), _p(reductors.contiguous(), torch.float32, 'reductors'),
+                                       _p(grouping.group_start), nel, rows, repsize, npcas, int(bool(transpose)), _p(out),
+                                       _stream(inp.device)), 'qmlb_pca_project')
+    return out
+
+
+def sorf_coefficients(u, D, normalisation, ntransforms):
+    u = u.contiguous()
+    D = D.contiguous()
+    n, N = u.shape
+    T, S, N2 = D.shape
+    if N2 != N or T < int(ntransforms):
+        raise RuntimeError("dmatrix shape does not match the input")
+    out = torch.empty(n, S, N, dtype=torch.float32, device=u.device)
+    check(_lib.load().qmlb_sorf_coefficients(_p(u, torch.float32, 'input'), _p(D, torch.float32, 'dmatrix'), n, N, S,
+                                             int(ntransforms), float(normalisation), _p(out), _stream(u.device)),
+          'qmlb_sorf_coefficients')
+    return out
+
+
+def sorf_coefficients_backward(grad, D, normalisation, ntransforms):
+    grad = grad.contiguous()
+    D = D.contiguous()
+    n, S, N = grad.shape
+    out = torch.empty(n, N, dtype=torch.float32, device=grad.device)
+    check(_lib.load().qmlb_sorf_coefficients_backward(_p(grad, torch.float32, 'grad'), _p(D, torch.float32, 'dmatrix'), n, N,
+                                                      S, int(ntransforms), float(normalisation), _p(out),
+                                                      _stream(grad.device)), 'qmlb_sorf_coefficients_backward')
+    return out
+
+
+def cos_features(coeffs, bias, nmol, batch_indexes):
+    coeffs = coeffs.contiguous()
+    n, F = coeffs.shape
+    out = torch.empty(int(nmol), F, dtype=torch.float32, device=coeffs.device)
+    check(_lib.load().qmlb_cos_features(_p(coeffs, torch.float32, 'coeffs'), _p(bias.contiguous(), torch.float32, 'b'),
+                                        _p(batch_indexes.contiguous(), torch.int32, 'batch_indexes'), n, F, int(nmol),
+                                        _p(out), _stream(coeffs.device)), 'qmlb_cos_features')
+    return out
+
+
+def cos_features_backward(grads, coeffs, bias, batch_indexes):
+    coeffs = coeffs.contiguous()
+    n, F = coeffs.shape
+    out = torch.empty(n, F, dtype=torch.float32, device=coeffs.device)
+    check(_lib.load().qmlb_cos_features_backward(_p(grads.contiguous(), torch.float32, 'grads'), _p(coeffs, torch.float32, 'coeffs'),
+                                                 _p(bias.contiguous(), torch.float32, 'b'),
+                                                 _p(batch_indexes.contiguous(), torch.int32, 'batch_indexes'), n, F, _p(out),
+                                                 _stream(coeffs.device)), 'qmlb_cos_features_backward')
+    return out
+
+
+def sorf_pack(Dmat, bias, alpha):
+    """Dmat f32[nel,T,S,N], bias f32[nel,S*N], alpha f32[S*N] -> opaque packed parameter buffer."""
+    Dmat = Dmat.contiguous().float()
+    nel, T, S, N = Dmat.shape
+    lib = _lib.load()
+    packed = torch.empty(lib.qmlb_sorf_pack_bytes(nel, N, S, T) // 4, dtype=torch.float32, device=Dmat.device)
+    check(lib.qmlb_sorf_pack(_p(Dmat, torch.float32, 'Dmat'), _p(bias.contiguous().float(), torch.float32, 'bias'),
+                             _p(alpha.contiguous().float(), torch.float32, 'alpha'), nel, N, S, T, _p(packed),
+                             _stream(Dmat.device)), 'qmlb_sorf_pack')
+    return packed
+
+
+def sorf_energy_grad(x, grouping, packed, N, S, T, sigma, fast_math=True):
+    rows = grouping.rows_cap
+    dev = x.device
+    atom_energy = torch.empty(rows, dtype=torch.float32, device=dev)
+    grad_x = torch.empty(rows, N, dtype=torch.float32, device=dev)
+    check(_lib.load().qmlb_sorf_energy_grad(_p(x, torch.float32, 'x'), _p(grouping.group_start), _p(grouping.slot_of_row),
+                                            grouping.nelements, rows, N, S, T, float(sigma), _p(packed), int(bool(fast_math)),
+                                            _p(atom_energy), _p(grad_x), _stream(dev)), 'qmlb_sorf_energy_grad')
+    return atom_energy, grad_x
+
+
+def sorf_predict(X, Z, atom_counts, fchl, elements, reductors, packed, S, T, sigma, cell=None, inv_cell=None,
+                 n_atoms_upper=None, fast_math=True):
+    """Energies ``[nb]`` and ``dE/dX [nb,A,3]`` through the fused pipeline (six kernel stages, no host sync)."""
+    X, Z, atom_counts, nb, A = _batch(X, Z, atom_counts)
+    nel, repsize, N = reductors.shape
+    g = group_by_element(Z, atom_counts, elements, n_atoms_upper)
+    rep = torch.empty(g.rows_cap, repsize, dtype=torch.float32, device=X.device)
+    fchl19_forward(X, Z, atom_counts, fchl, cell, inv_cell, row_of_slot=g.row_of_slot, out=rep)
+    x = pca_project(rep, reductors, g, transpose=False)
+    atom_energy, grad_x = sorf_energy_grad(x, g, packed, N, S, T, sigma, fast_math)
+    pca_project(grad_x, reductors, g, transpose=True, out=rep)  # rep buffer reused for d/d(rep)
+    grad_X, energy = fchl19_backward(X, Z, atom_counts, fchl, rep, cell, inv_cell, row_of_slot=g.row_of_slot,
+                                     atom_energy=atom_energy)
+    return energy, grad_X

@@ -1,0 +1,338 @@
+// Fused SORF energy + gradient kernel (sm_100a).
+//
+// Replaces, per atom row, the upstream chain
+//   get_SORF_coefficients -> get_cos_features -> matmul(Ztest, alpha)            (models/hadamard_features.py:113-121)
+// and its autograd backward (cuda/torchscript/SORF.cpp:89-101,121-133) by one pass that never writes the
+// [atoms, nstacks*npcas] coefficient tensor: for every stack s
+//   u = (H D_{T-1,s} ... H D_{0,s}) x ;  arg = scale*u + b_s ;  E += alpha_s . cos(arg) ;
+//   g = -alpha_s sin(arg) ;  grad_x += (D_0 H ... D_{T-1} H) g            (scale applied once at the end)
+// with scale = (sqrt(N)/sigma) * N^(-T/2).
+//
+// Data layout.  A vector of N = 2^n floats is held by L = N/16 lanes, 16 registers per lane; a warp therefore
+// works on V = 32/L stacks of the same atom at once.  The fast Walsh-Hadamard transform runs 4 butterfly stages
+// in registers, transposes the 16 x L tile through a per-warp shared-memory slab (128-bit stores, conflict-free
+// 32-bit loads, row stride 20 floats), runs the remaining stages in registers again and, for N = 512 only, one
+// warp-shuffle stage for the last bit.  The transposed register order ("layout B") is kept through the
+// cos/sin step, so the backward transform starts from it and ends in the natural order ("layout A"):
+// two transpositions per stack in total.  Sign diagonals, bias and weights are pre-permuted once per model by
+// qmlb_sorf_pack so that every lane reads 16 consecutive floats.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int ROWSTRIDE = 20;  // floats per 16-element row in the transposition slab
+
+template <int LOG2N>
+struct Cfg {
+    static constexpr int N = 1 << LOG2N;
+    static constexpr int LB = LOG2N - 4;              // lane bits of a vector
+    static constexpr int L = 1 << LB;                 // lanes per vector
+    static constexpr int V = 32 / L;                  // vectors (stacks) per warp
+    static constexpr int LBT = LB > 4 ? 4 : LB;       // bits exchanged by the transposition
+    static constexpr int ROWS = L;                    // rows of 16 in the slab
+    static constexpr int RAW = ROWS * ROWSTRIDE + (ROWS > 16 ? 16 : 0);
+    // slab stride: distinct bank ranges for the V vectors of a warp (V*L = 32 lanes read L consecutive words each)
+    static constexpr int SLAB = V == 1 ? RAW : (V == 2 ? RAW + 16 : (V == 4 ? RAW + 8 : RAW + 4));
+    static constexpr int WARP_FLOATS = V * SLAB;
+};
+
+// position (lane-in-vector * 16 + register) -> element index n, for the transposed layout B
+__host__ __device__ inline int layoutB_n(int log2n, int pos) {
+    const int LB = log2n - 4;
+    const int l = pos >> 4, e = pos & 15;
+    if (LB <= 4) {
+        const int L = 1 << LB;
+        return (e & (L - 1)) * 16 + ((e >> LB) << LB) + l;
+    }
+    return ((l & 16) | e) * 16 + (l & 15);
+}
+
+__device__ __forceinline__ void butterfly(float &a, float &b) {
+    const float t = a;
+    a = t + b;
+    b = t - b;
+}
+
+template <int BITS>
+__device__ __forceinline__ void fwht_regs(float (&u)[16]) {
+#pragma unroll
+    for (int h = 1; h < (1 << BITS); h <<= 1)
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if ((i & h) == 0) butterfly(u[i], u[i | h]);
+}
+
+template <int LOG2N>
+struct Xpose {
+    using C = Cfg<LOG2N>;
+    // shared-memory offset of lane l's row in layout A, and of lane l's column base in layout B
+    __device__ static __forceinline__ int a_base(int l) { return l * ROWSTRIDE + (l >> 4) * 16; }
+    __device__ static __forceinline__ int b_base(int l) {
+        if (C::LB <= 4) return l;
+        return (l >> 4) * (16 * ROWSTRIDE + 16) + (l & 15);
+    }
+    // constant part of the layout-B address of register e
+    __device__ static __forceinline__ constexpr int b_const(int e) {
+        return C::LB <= 4 ? (e & (C::L - 1)) * ROWSTRIDE + ((e >> C::LB) << C::LB) : e * ROWSTRIDE;
+    }
+    __device__ static __forceinline__ void a_to_b(float (&u)[16], float *slab, int l) {
+        float4 *w = reinterpret_cast<float4 *>(slab + a_base(l));
+#pragma unroll
+        for (int q = 0; q < 4; ++q) w[q] = make_float4(u[4 * q], u[4 * q + 1], u[4 * q + 2], u[4 * q + 3]);
+        __syncwarp();
+        const float *r = slab + b_base(l);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) u[e] = r[b_const(e)];
+        __syncwarp();
+    }
+    __device__ static __forceinline__ void b_to_a(float (&u)[16], float *slab, int l) {
+        float *w = slab + b_base(l);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) w[b_const(e)] = u[e];
+        __syncwarp();
+        const float4 *r = reinterpret_cast<const float4 *>(slab + a_base(l));
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float4 t = r[q];
+            u[4 * q] = t.x; u[4 * q + 1] = t.y; u[4 * q + 2] = t.z; u[4 * q + 3] = t.w;
+        }
+        __syncwarp();
+    }
+};
+
+// butterfly across lanes l and l^16 (only N = 512)
+__device__ __forceinline__ void lane16_stage(float (&u)[16], int lane) {
+    const float sgn = (lane & 16) ? -1.0f : 1.0f;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+        const float o = __shfl_xor_sync(QMLB_FULL_MASK, u[e], 16);
+        u[e] = fmaf(sgn, u[e], o);
+    }
+}
+
+// One unnormalised FWHT; flips the layout (A -> B when from_a, else B -> A).
+template <int LOG2N>
+__device__ __forceinline__ void fwht_flip(float (&u)[16], float *slab, int l, int lane, bool from_a) {
+    using C = Cfg<LOG2N>;
+    if (C::LB == 0) {  // N = 16: everything in registers, layouts coincide
+        fwht_regs<4>(u);
+        return;
+    }
+    if (from_a) {
+        fwht_regs<4>(u);
+        Xpose<LOG2N>::a_to_b(u, slab, l);
+        fwht_regs<C::LBT>(u);
+        if (C::LB == 5) lane16_stage(u, lane);
+    } else {
+        if (C::LB == 5) lane16_stage(u, lane);
+        fwht_regs<C::LBT>(u);
+        Xpose<LOG2N>::b_to_a(u, slab, l);
+        fwht_regs<4>(u);
+    }
+}
+
+__device__ __forceinline__ void load16(float (&v)[16], const float *p) {
+    const float4 *q = reinterpret_cast<const float4 *>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float4 t = __ldg(q + i);
+        v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+    }
+}
+
+template <int LOG2N, bool FAST, int TT>
+__global__ void __launch_bounds__(WARPS * 32)
+sorf_energy_grad_kernel(const float *__restrict__ x, const int *__restrict__ group_start,
+                        const int *__restrict__ slot_of_row, int nel, int S, int T_rt, float scale,
+                        const float *__restrict__ Dp, const float *__restrict__ bp, const float *__restrict__ ap,
+                        float *__restrict__ atom_energy, float *__restrict__ grad_x) {
+    using C = Cfg<LOG2N>;
+    constexpr int N = C::N;
+    extern __shared__ __align__(16) float smem[];
+    const int T = TT > 0 ? TT : T_rt;  // compile-time trip count for the common single-transform model
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane / C::L, l = lane % C::L;  // vector within the warp, lane within the vector
+    float *slab = smem + warp * C::WARP_FLOATS + g * C::SLAB;
+
+    const long row = (long)blockIdx.x * WARPS + warp;
+    if (row >= group_start[nel]) return;
+    if (slot_of_row[row] < 0) {  // padding row of an element group
+        if (lane == 0) atom_energy[row] = 0.f;
+        return;
+    }
+    int el = 0;
+    while (el + 1 < nel && row >= group_start[el + 1]) ++el;
+
+    float xr[16], gx[16];
+    load16(xr, x + (size_t)row * N + l * 16);
+#pragma unroll
+    for (int e = 0; e < 16; ++e) gx[e] = 0.f;
+    float eacc = 0.f;
+
+    const size_t pos = (size_t)l * 16;
+    const float *Dp_e = Dp + (size_t)el * S * T * N;
+    const float *bp_e = bp + (size_t)el * S * N;
+
+    for (int s0 = 0; s0 < S; s0 += C::V) {
+        const int s = s0 + g;
+        const bool valid = s < S;
+        const int sc = valid ? s : S - 1;
+        const float *Ds = Dp_e + (size_t)sc * T * N + pos;
+        float u[16], c[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) u[e] = xr[e];
+        bool in_a = true;
+#pragma unroll
+        for (int m = 0; m < T; ++m) {
+            load16(c, Ds + (size_t)m * N);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) u[e] *= c[e];
+            fwht_flip<LOG2N>(u, slab, l, lane, in_a);
+            in_a = !in_a;
+        }
+        {   // features: energy contribution and d/d(arg), in the layout the forward transform ended in
+            float a[16];
+            load16(c, bp_e + (size_t)sc * N + pos);
+            load16(a, ap + (size_t)sc * N + pos);
+            const float vf = valid ? 1.0f : 0.0f;
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                const float arg = fmaf(u[e], scale, c[e]);
+                float sn, cs;
+                if (FAST) __sincosf(arg, &sn, &cs);
+                else sincosf(arg, &sn, &cs);
+                const float al = a[e] * vf;
+                eacc = fmaf(al, cs, eacc);
+                u[e] = -al * sn;
+            }
+        }
+#pragma unroll
+        for (int m = T - 1; m >= 0; --m) {
+            fwht_flip<LOG2N>(u, slab, l, lane, in_a);
+            in_a = !in_a;
+            load16(c, Ds + (size_t)m * N);
+            if (m > 0) {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) u[e] *= c[e];
+            } else {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) gx[e] = fmaf(u[e], c[e], gx[e]);
+            }
+        }
+    }
+
+    // sum the V stacks processed side by side, then one store per atom
+#pragma unroll
+    for (int off = C::L; off < 32; off <<= 1)
+#pragma unroll
+        for (int e = 0; e < 16; ++e) gx[e] += __shfl_xor_sync(QMLB_FULL_MASK, gx[e], off);
+    eacc = warp_sum(eacc);
+    if (g == 0) {
+        float4 *dst = reinterpret_cast<float4 *>(grad_x + (size_t)row * N + l * 16);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            dst[q] = make_float4(gx[4 * q] * scale, gx[4 * q + 1] * scale, gx[4 * q + 2] * scale, gx[4 * q + 3] * scale);
+    }
+    if (lane == 0) atom_energy[row] = eacc;
+}
+
+__global__ void sorf_pack_kernel(const float *__restrict__ Dmat, const float *__restrict__ bias,
+                                 const float *__restrict__ alpha, int nel, int log2n, int S, int T,
+                                 float *__restrict__ Dp, float *__restrict__ bp, float *__restrict__ ap) {
+    const int N = 1 << log2n;
+    const size_t nD = (size_t)nel * S * T * N, nB = (size_t)nel * S * N, nA = (size_t)S * N;
+    const float normf = sqrtf(2.0f / (float)((size_t)S * N));
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nD + nB + nA; i += (size_t)gridDim.x * blockDim.x) {
+        if (i < nD) {  // Dp[el][s][m][pos] <- Dmat[el][m][s][n]
+            const int p = (int)(i % N);
+            const int m = (int)((i / N) % T);
+            const int s = (int)((i / ((size_t)N * T)) % S);
+            const int el = (int)(i / ((size_t)N * T * S));
+            const int n = (m & 1) ? layoutB_n(log2n, p) : p;
+            Dp[i] = Dmat[(((size_t)el * T + m) * S + s) * N + n];
+        } else if (i < nD + nB) {
+            const size_t k = i - nD;
+            const int p = (int)(k % N);
+            const size_t es = k / N;  // el*S + s
+            const int n = (T & 1) ? layoutB_n(log2n, p) : p;
+            bp[k] = bias[es * N + n];
+        } else {
+            const size_t k = i - nD - nB;
+            const int p = (int)(k % N);
+            const size_t s = k / N;
+            const int n = (T & 1) ? layoutB_n(log2n, p) : p;
+            ap[k] = alpha[s * N + n] * normf;
+        }
+    }
+}
+
+int ilog2_exact(int n) {
+    int l = 0;
+    while ((1 << l) < n) ++l;
+    return (1 << l) == n ? l : -1;
+}
+
+template <int LOG2N>
+int launch_fused(const float *x, const int *group_start, const int *slot_of_row, int nel, size_t rows_cap, int S, int T,
+                 float scale, const float *Dp, const float *bp, const float *ap, int fast, float *atom_energy,
+                 float *grad_x, cudaStream_t st) {
+    using C = Cfg<LOG2N>;
+    const size_t smem = sizeof(float) * WARPS * C::WARP_FLOATS;
+    const unsigned grid = (unsigned)((rows_cap + WARPS - 1) / WARPS);
+#define QMLB_LAUNCH(FASTV, TTV)                                                                                      \
+    sorf_energy_grad_kernel<LOG2N, FASTV, TTV><<<grid, WARPS * 32, smem, st>>>(x, group_start, slot_of_row, nel, S, T, \
+                                                                               scale, Dp, bp, ap, atom_energy, grad_x)
+    if (T == 1) {
+        if (fast) QMLB_LAUNCH(true, 1); else QMLB_LAUNCH(false, 1);
+    } else {
+        if (fast) QMLB_LAUNCH(true, 0); else QMLB_LAUNCH(false, 0);
+    }
+#undef QMLB_LAUNCH
+    return qmlb::check_launch("qmlb_sorf_energy_grad");
+}
+
+}  // namespace
+
+extern "C" size_t qmlb_sorf_pack_bytes(int nelements, int N, int S, int T) {
+    return sizeof(float) * ((size_t)nelements * S * T * N + (size_t)nelements * S * N + (size_t)S * N);
+}
+
+extern "C" int qmlb_sorf_pack(const float *Dmat, const float *bias, const float *alpha, int nelements, int N, int S,
+                              int T, void *packed, qmlb_stream_t stream) {
+    QMLB_REQUIRE(Dmat && bias && alpha && packed, "qmlb_sorf_pack: null tensor");
+    const int log2n = ilog2_exact(N);
+    QMLB_REQUIRE(log2n >= 4 && log2n <= 9, "qmlb_sorf_pack: npcas must be a power of two in [16, 512], got %d", N);
+    QMLB_REQUIRE(nelements > 0 && S > 0 && T > 0, "qmlb_sorf_pack: bad sizes");
+    float *Dp = static_cast<float *>(packed);
+    float *bp = Dp + (size_t)nelements * S * T * N;
+    float *ap = bp + (size_t)nelements * S * N;
+    sorf_pack_kernel<<<592, 256, 0, qmlb::as_stream(stream)>>>(Dmat, bias, alpha, nelements, log2n, S, T, Dp, bp, ap);
+    return qmlb::check_launch("qmlb_sorf_pack");
+}
+
+extern "C" int qmlb_sorf_energy_grad(const float *x, const int *group_start, const int *slot_of_row, int nelements,
+                                     size_t rows_cap, int N, int S, int T, float sigma, const void *packed,
+                                     int fast_math, float *atom_energy, float *grad_x, qmlb_stream_t stream) {
+    QMLB_REQUIRE(x && group_start && slot_of_row && packed && atom_energy && grad_x, "qmlb_sorf_energy_grad: null tensor");
+    const int log2n = ilog2_exact(N);
+    QMLB_REQUIRE(log2n >= 4 && log2n <= 9, "qmlb_sorf_energy_grad: npcas must be a power of two in [16, 512], got %d", N);
+    QMLB_REQUIRE(nelements > 0 && S > 0 && T > 0 && sigma > 0.f, "qmlb_sorf_energy_grad: bad sizes");
+    if (rows_cap == 0) return QMLB_OK;
+    const float *Dp = static_cast<const float *>(packed);
+    const float *bp = Dp + (size_t)nelements * S * T * N;
+    const float *ap = bp + (size_t)nelements * S * N;
+    // coeff_normalisation sqrt(N)/sigma (models/hadamard_features.py:93) times N^(-1/2) per transform
+    const float scale = (float)(sqrt((double)N) / (double)sigma * pow((double)N, -0.5 * (double)T));
+    cudaStream_t st = qmlb::as_stream(stream);
+    switch (log2n) {
+        case 4: return launch_fused<4>(x, group_start, slot_of_row, nelements, rows_cap, S, T, scale, Dp, bp, ap, fast_math, atom_energy, grad_x, st);
+        case 5: return launch_fused<5>(x, group_start, slot_of_row, nelements, rows_cap, S, T, scale, Dp, bp, ap, fast_math, atom_energy, grad_x, st);
+        case 6: return launch_fused<6>(x, group_start, slot_of_row, nelements, rows_cap, S, T, scale, Dp, bp, ap, fast_math, atom_energy, grad_x, st);
+        case 7: return launch_fused<7>(x, group_start, slot_of_row, nelements, rows_cap, S, T, scale, Dp, bp, ap, fast_math, atom_energy, grad_x, st);
+        case 8: return launch_fused<8>(x, group_start, slot_of_row, nelements, rows_cap, S, T, scale, Dp, bp, ap, fast_math, atom_energy, grad_x, st);
+        default: return launch_fused<9>(x, group_start, slot_of_row, nelements, rows_cap, S, T, scale, Dp, bp, ap, fast_math, atom_energy, grad_x, st);
+    }
+}
