@@ -1,0 +1,321 @@
+#!/usr/bin/env python
+"""Benchmark of the energy+force prediction hot path (FCHL19 -> PCA -> SORF -> energy -> forces).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--conformers M]
+
+Workload (``config.workload`` = "c1"): 10,000 seeded conformers of a 21-atom C9H8O4 molecule per GPU, FCHL19 with
+rcut 6.0 / nRs2 24 / nRs3 22, npcas 256, nstacks 256 (65,536 SORF features), fp32.  One step = one pass of the
+whole prediction path over that batch.  With N > 1 (torchrun, one rank per GPU) every rank predicts its own batch
+and no data-path collective is involved (weak scaling); the reported value is molecules of all ranks divided by the
+slowest rank's time.
+
+Prints ONE JSON line.  ``value`` is device-timed with the batch resident in HBM; ``e2e`` goes through the public
+model API from pinned host buffers and back; ``roofline`` covers the dominant kernel (fused SORF energy/gradient)
+timed live with CUDA events; ``cpu_baseline`` is the CPU oracle timed on a bounded sample (rank 0, N = 1 only).
+``--impl reference`` times the CPU oracle alone (the upstream project has no CPU implementation of this path, so the
+oracle port is the CPU reference).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+NPCAS, NSTACKS, SIGMA = 256, 256, 2.0
+SPECIES = [1, 6, 8]
+KERNELS_PER_STEP = 8  # count, scan, assign, fchl forward, pca, sorf fused, pca^T, fchl backward
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=10)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--conformers', type=int, default=10000)
+    ap.add_argument('--cpu-sample', type=int, default=256, help='conformers per CPU-baseline step')
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    return ap.parse_args()
+
+
+def workload(nconf, seed):
+    from qml_lightning_b200.utils import synthetic as syn
+    X, Z, counts = syn.conformers(seed, syn.C1_CHARGES, nconf)
+    return X, Z, counts
+
+
+def algorithmic_bytes_per_atom(repsize):
+    """Inter-stage tensors of the unfused chain written once and read once, plus 40 bytes of input/output."""
+    F = NPCAS * NSTACKS
+    return 4 * (2 * F + 4 * repsize + 4 * NPCAS) + 40
+
+
+def sorf_kernel_bytes_per_atom():
+    """Dominant kernel: coefficient tensor out and back, projected input in, gradient out, atom energy."""
+    F = NPCAS * NSTACKS
+    return 4 * (2 * F + 2 * NPCAS) + 4
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,'
+         'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, index):
+        self.index, self.lines, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.Q}', '--format=csv,noheader,nounits', '-lms', '100',
+                                          '-i', str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(',')]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap'), f[5:9]):
+                if val.lower().startswith('active'):
+                    reasons.add(name)
+        busy = [s for s in sm if s > 0.5 * max(mx)] if sm else []
+        use = busy or sm
+        return {'sm_mhz': float(np.median(use)) if use else None, 'sm_max_mhz': max(mx) if mx else None,
+                'reasons': sorted(reasons), 'samples': len(sm)}
+
+
+def build_model(device, X, Z, counts):
+    """Model through the public API: FCHLCuda + HadamardFeaturesModel, reductors from SVD of our own representation."""
+    import qml_lightning_b200 as q
+    np.random.seed(1234)
+    torch.manual_seed(1234)
+    rep = q.FCHLCuda(species=np.array(SPECIES), rcut=6.0, nRs2=24, nRs3=22, eta2=0.32, eta3=2.7, two_body_decay=1.8,
+                     three_body_weight=13.4, three_body_decay=0.57, device=device)
+    model = q.HadamardFeaturesModel(rep=rep, elements=np.array(SPECIES), ntransforms=1, sigma=SIGMA, llambda=1e-5,
+                                    npcas=NPCAS, nstacks=NSTACKS, nbatch_train=64, nbatch_test=len(X))
+    sub = slice(0, 64)
+    model.get_reductors([x for x in X[sub]], [z for z in Z[sub]], npcas=NPCAS, npca_choice=512, nsamples=512, print_info=False)
+    model.set_alpha(torch.from_numpy(np.random.default_rng(5).normal(size=model.nfeatures()).astype(np.float32)))
+    return rep, model
+
+
+def cpu_oracle_rate(model, rep, X, Z, counts, nsample, steps=1, warmup=0):
+    """Molecules/s of the torch-CPU oracle (fp32, all host threads) on the first ``nsample`` conformers."""
+    from oracle import FCHLParams, energy_and_forces
+    torch.set_num_threads(os.cpu_count())
+    p = FCHLParams(species=SPECIES, rcut=6.0, nRs2=24, nRs3=22, eta2=0.32, eta3=2.7, two_body_decay=1.8,
+                   three_body_weight=13.4, three_body_decay=0.57)
+    m = dict(kind='sorf', elements=SPECIES, reductors=model.reductors.cpu(), Dmat=model.Dmat.cpu(), bias=model.bias.cpu(),
+             alpha=model.alpha.cpu(), sigma=SIGMA, ntransforms=1)
+    Xs, Zs, cs = (torch.from_numpy(a[:nsample]) for a in (X, Z, counts))
+    times = []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        energy_and_forces(Xs, Zs, cs, p, m, batch=16, dtype=torch.float32)
+        times.append(time.perf_counter() - t0)
+    dt = float(np.mean(times[warmup:]))
+    return nsample / dt, dt
+
+
+def run_reference(args, rank, world):
+    """CPU reference arm: the oracle port on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    X, Z, counts = workload(max(args.cpu_sample, 64), 1001)
+    dev = torch.device('cuda', 0) if torch.cuda.is_available() else None
+    if dev is None:
+        print(json.dumps({'impl': 'reference', 'unavailable': 'model set-up (reductors) needs the CUDA representation kernel'}))
+        return
+    rep, model = build_model(dev, X, Z, counts)
+    rate, dt = cpu_oracle_rate(model, rep, X, Z, counts, args.cpu_sample, steps=args.steps, warmup=min(args.warmup, 1))
+    line = {
+        'impl': 'reference', 'metric': 'energy+force predictions', 'value': rate, 'unit': 'molecules/s', 'n_gpus': args.gpus,
+        'steps': args.steps, 'warmup': min(args.warmup, 1), 'ms_per_step': dt * 1e3, 'higher_is_better': True,
+        'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'config': {'workload': 'c1', 'atoms_per_molecule': 21, 'npcas': NPCAS, 'nstacks': NSTACKS,
+                   'features': NPCAS * NSTACKS, 'conformers_per_step': args.cpu_sample},
+        'cpu_baseline': {'value': rate, 'unit': 'molecules/s', 'cores': os.cpu_count(), 'kind': 'port',
+                         'sample': f'{args.cpu_sample} conformers of the c1 workload per step, torch CPU fp32 oracle'},
+        'e2e': {'value': rate, 'unit': 'molecules/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get('RANK', 0))
+    world = int(os.environ.get('WORLD_SIZE', 1))
+    local = int(os.environ.get('LOCAL_RANK', 0))
+    if args.impl == 'reference':
+        run_reference(args, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit('bench.py needs a CUDA device: the prediction path has no CPU fallback')
+    dev = torch.device('cuda', local)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group('nccl', device_id=dev)
+
+    from qml_lightning_b200 import cabi
+    X, Z, counts = workload(args.conformers, 1001 + rank)       # every rank owns its own molecules
+    rep, model = build_model(dev, X, Z, counts)
+    nconf, A = Z.shape
+    natoms = int(counts.sum())
+    kp = rep.kernel_params(dev)
+    Xd, Zd, cd = (torch.from_numpy(a).to(dev) for a in (X, Z, counts))
+    atomIDs = torch.arange(A, dtype=torch.int32, device=dev).repeat(nconf)
+    molIDs = torch.arange(nconf, dtype=torch.int32, device=dev).repeat_interleave(A)
+    flush = torch.empty(512 * 1024 * 1024, dtype=torch.uint8, device=dev)   # > 126 MB L2
+    E = torch.empty(nconf, dtype=torch.float32, device=dev)
+    G = torch.empty(nconf, A, 3, dtype=torch.float32, device=dev)
+
+    def step():
+        cabi.sorf_predict(Xd, Zd, cd, kp, model.species, model.reductors, model.packed, NSTACKS, 1, SIGMA,
+                          n_atoms_upper=natoms, fast_math=model.fast_math, energy=E, grad_X=G)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for s, e in evs:
+        flush.fill_(1)          # evict L2 between steps (outside the timed events)
+        s.record()
+        step()
+        e.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = float(np.mean([s.elapsed_time(e) for s, e in evs]))
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    value = world * nconf / (ms_max * 1e-3)
+
+    # ---- dominant kernel alone, CUDA events on the launching stream -------------------------------------------------
+    g = cabi.group_by_element(Zd, cd, model.species, natoms)
+    repbuf = torch.empty(g.rows_cap, rep.get_repsize(), dtype=torch.float32, device=dev)
+    cabi.fchl19_forward(Xd, Zd, cd, kp, row_of_slot=g.row_of_slot, out=repbuf)
+    xproj = cabi.pca_project(repbuf, model.reductors, g)
+    kev = []
+    for _ in range(max(3, min(args.steps, 10))):
+        flush.fill_(1)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        cabi.sorf_energy_grad(xproj, g, model.packed, NPCAS, NSTACKS, 1, SIGMA, model.fast_math)
+        e.record()
+        kev.append((s, e))
+    torch.cuda.synchronize()
+    k_ms = float(np.mean([s.elapsed_time(e) for s, e in kev]))
+
+    # ---- end to end through the public API: pinned host -> device -> predict_opt -> host ----------------------------
+    hX, hZ, hc = (torch.from_numpy(a).pin_memory() for a in (X, Z, counts))
+    hA, hM = atomIDs.cpu().pin_memory(), molIDs.cpu().pin_memory()
+    hE = torch.empty(nconf, dtype=torch.float32).pin_memory()
+    hF = torch.empty(nconf, A, 3, dtype=torch.float32).pin_memory()
+    h2d = sum(t_.numel() * t_.element_size() for t_ in (hX, hZ, hc, hA, hM))
+    d2h = hE.numel() * 4 + hF.numel() * 4
+
+    def e2e_step():
+        dX, dZ, dc, dA, dM = (t_.to(dev, non_blocking=True) for t_ in (hX, hZ, hc, hA, hM))
+        en, fo = model.predict_opt(dX, dZ, dA, dM, dc, forces=True)
+        hE.copy_(en, non_blocking=True)
+        hF.copy_(fo, non_blocking=True)
+
+    for _ in range(args.warmup):
+        e2e_step()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = world * nconf / (float(t.item()) * 1e-3)
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_src = {}, 'fallback'
+    pk_path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(pk_path):
+        with open(pk_path) as fh:
+            peaks = json.load(fh)
+        peak_src = 'measured'
+    hbm = float(peaks.get('hbm_gbs', 6650.0))
+    k_bytes = sorf_kernel_bytes_per_atom() * natoms
+    achieved = k_bytes / (k_ms * 1e-3) / 1e9
+    pipe_bytes = algorithmic_bytes_per_atom(rep.get_repsize()) * natoms * world
+    pipe_gbs = pipe_bytes / (ms_max * 1e-3) / 1e9
+    line = {
+        'metric': 'energy+force predictions', 'value': value, 'unit': 'molecules/s', 'n_gpus': world, 'steps': args.steps,
+        'warmup': args.warmup, 'ms_per_step': ms_max, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+        'dtype': 'f32', 'data': 'synthetic',
+        'config': {'workload': 'c1', 'molecules_per_gpu': nconf, 'atoms_per_molecule': A, 'species': SPECIES, 'npcas': NPCAS,
+                   'nstacks': NSTACKS, 'features': NPCAS * NSTACKS, 'parallelism': f'molecule shards x{world}, no collective',
+                   'l2': 'flushed between steps (512 MB write outside the timed events); per-step workspace > L2',
+                   'fast_math': bool(model.fast_math)},
+        'e2e': {'value': e2e_value, 'unit': 'molecules/s', 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h},
+        'gpu_launches': KERNELS_PER_STEP * args.steps,
+        'clocks': clocks,
+        'roofline': {'bound': 'hbm', 'kernel': 'sorf_energy_grad_kernel', 'achieved': achieved, 'peak': hbm, 'unit': 'GB/s',
+                     'frac': achieved / hbm, 'traffic': SORF_KERNEL_DRAM_BYTES_PER_ATOM * natoms if SORF_KERNEL_DRAM_BYTES_PER_ATOM else None,
+                     'peak_source': peak_src, 'kernel_ms': k_ms, 'algorithmic_bytes_per_launch': k_bytes,
+                     'pipeline_hbm_equivalent_gbs': pipe_gbs / world, 'pipeline_frac': pipe_gbs / world / hbm},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        rate, dt = cpu_oracle_rate(model, rep, X, Z, counts, args.cpu_sample)
+        line['cpu_baseline'] = {'value': rate, 'unit': 'molecules/s', 'cores': os.cpu_count(), 'kind': 'port',
+                                'sample': f'{args.cpu_sample} conformers of the c1 workload, torch CPU fp32 oracle, {dt:.1f} s'}
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+# DRAM bytes per atom of the fused SORF kernel from the ncu capture summarised in
+# profiles/sorf_energy_grad_kernel_c1.md (dram__bytes_read.sum + dram__bytes_write.sum divided by the atoms of the
+# captured launch); None until a capture exists.
+SORF_KERNEL_DRAM_BYTES_PER_ATOM = None
+
+if __name__ == '__main__':
+    main()

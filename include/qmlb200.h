@@ -178,6 +178,22 @@ int qmlb_sorf_energy_grad(const float *x, const int *group_start, const int *slo
                           size_t rows_cap, int N, int S, int T, float sigma, const void *packed, int fast_math,
                           float *atom_energy, float *grad_x, qmlb_stream_t stream);
 
+/* ---- whole-batch prediction ----------------------------------------------------------------- */
+
+/* HadamardFeaturesModel.forward + torch.autograd.grad(-E.sum(), X) (models/hadamard_features.py:82-123, 157-162;
+ * predict_opt :125-179) as one call: energy f32[nb] (without self energies, like upstream forward) and
+ * grad_X f32[nb,A,3] = dE/dX (forces are -grad_X).  All six stages run on `stream` inside `workspace`
+ * (qmlb_predict_workspace_bytes bytes, 256-byte aligned device memory); nothing is allocated and the host never
+ * waits for the device.  n_atoms_upper is an upper bound of the number of real atoms (nb*A if unknown; the length
+ * of upstream's atomIDs tensor when available).  elements f32[nelements] are the model's elements,
+ * reductors f32[nelements, repsize, npcas], packed from qmlb_sorf_pack. */
+size_t qmlb_predict_workspace_bytes(int nb, int A, size_t n_atoms_upper, int nelements, int repsize, int npcas);
+int qmlb_sorf_predict(const float *X, const float *Z, const int *atom_counts, int nb, int A, const qmlb_fchl_params *p,
+                      const float *cell, const float *inv_cell, const float *elements, int nelements,
+                      const float *reductors, int npcas, const void *packed, int S, int T, float sigma, int fast_math,
+                      size_t n_atoms_upper, void *workspace, size_t workspace_bytes, float *energy, float *grad_X,
+                      qmlb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -43,6 +43,10 @@ SIGNATURES = {
     'qmlb_sorf_pack_bytes': (c_size_t, [c_int, c_int, c_int, c_int]),
     'qmlb_sorf_pack': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     'qmlb_sorf_energy_grad': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    'qmlb_predict_workspace_bytes': (c_size_t, [c_int, c_int, c_size_t, c_int, c_int, c_int]),
+    'qmlb_sorf_predict': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, P, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                  c_int, c_void_p, c_int, c_int, c_float, c_int, c_size_t, c_void_p, c_size_t, c_void_p,
+                                  c_void_p, c_void_p]),
 }
 
 _lib = None

@@ -54,7 +54,7 @@ def build_native(verbose=False, ptxas_info=False):
             _run(cmd, verbose)
         objs.append(obj)
     if _newer(objs, NATIVE_LIB):
-        _run([_nvcc(), '-shared', '-o', NATIVE_LIB] + objs + ['-lcudart', '-lcublas'], verbose)
+        _run([_nvcc(), '-shared', '-gencode', 'arch=compute_100a,code=sm_100a', '-o', NATIVE_LIB] + objs + ['-lcudart', '-lcublas'], verbose)
     return NATIVE_LIB
 
 

@@ -253,9 +253,9 @@ def sorf_energy_grad(x, grouping, packed, N, S, T, sigma, fast_math=True):
     return atom_energy, grad_x
 
 
-def sorf_predict(X, Z, atom_counts, fchl, elements, reductors, packed, S, T, sigma, cell=None, inv_cell=None,
-                 n_atoms_upper=None, fast_math=True):
-    """Energies ``[nb]`` and ``dE/dX [nb,A,3]`` through the fused pipeline (six kernel stages, no host sync)."""
+def sorf_predict_staged(X, Z, atom_counts, fchl, elements, reductors, packed, S, T, sigma, cell=None, inv_cell=None,
+                        n_atoms_upper=None, fast_math=True):
+    """Same result as ``sorf_predict`` through the individual stage entry points (used by tests and profiling)."""
     X, Z, atom_counts, nb, A = _batch(X, Z, atom_counts)
     nel, repsize, N = reductors.shape
     g = group_by_element(Z, atom_counts, elements, n_atoms_upper)
@@ -266,4 +266,40 @@ def sorf_predict(X, Z, atom_counts, fchl, elements, reductors, packed, S, T, sig
     pca_project(grad_x, reductors, g, transpose=True, out=rep)  # rep buffer reused for d/d(rep)
     grad_X, energy = fchl19_backward(X, Z, atom_counts, fchl, rep, cell, inv_cell, row_of_slot=g.row_of_slot,
                                      atom_energy=atom_energy)
+    return energy, grad_X
+
+
+_workspaces = {}
+
+
+def _workspace(device, nbytes):
+    """Grow-only per-device scratch buffer, so steady-state prediction allocates nothing."""
+    ws = _workspaces.get(device)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(int(nbytes * 1.1) + 256, dtype=torch.uint8, device=device)
+        _workspaces[device] = ws
+    return ws
+
+
+def sorf_predict(X, Z, atom_counts, fchl, elements, reductors, packed, S, T, sigma, cell=None, inv_cell=None,
+                 n_atoms_upper=None, fast_math=True, energy=None, grad_X=None):
+    """Energies ``[nb]`` and ``dE/dX [nb,A,3]`` through ``qmlb_sorf_predict`` (one C call, no host sync)."""
+    X, Z, atom_counts, nb, A = _batch(X, Z, atom_counts)
+    cell, inv_cell = _cells(cell, inv_cell)
+    nel, repsize, N = reductors.shape
+    lib = _lib.load()
+    upper = nb * A if n_atoms_upper is None else int(n_atoms_upper)
+    need = lib.qmlb_predict_workspace_bytes(nb, A, upper, nel, repsize, N)
+    ws = _workspace(X.device, need)
+    if energy is None:
+        energy = torch.empty(nb, dtype=torch.float32, device=X.device)
+    if grad_X is None:
+        grad_X = torch.empty(nb, A, 3, dtype=torch.float32, device=X.device)
+    pc = fchl.c()
+    check(lib.qmlb_sorf_predict(_p(X, torch.float32, 'coordinates'), _p(Z, torch.float32, 'charges'),
+                                _p(atom_counts, torch.int32, 'atom_counts'), nb, A, ctypes.byref(pc), _p(cell), _p(inv_cell),
+                                _p(elements.contiguous(), torch.float32, 'elements'), nel,
+                                _p(reductors.contiguous(), torch.float32, 'reductors'), N, _p(packed), int(S), int(T),
+                                float(sigma), int(bool(fast_math)), upper, _p(ws), ws.numel(), _p(energy), _p(grad_X),
+                                _stream(X.device)), 'qmlb_sorf_predict')
     return energy, grad_X

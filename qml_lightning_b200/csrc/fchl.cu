@@ -18,7 +18,7 @@ namespace {
 
 constexpr int FCHL_WARPS = 8;
 constexpr int FCHL_THREADS = FCHL_WARPS * 32;
-constexpr float ZETA2 = 0.014384498882876630f;  // 2 * exp(-pi^2 / 2)
+constexpr float ZETA2 = 0.014383766711652736f;  // 2 * exp(-pi^2 / 2)
 
 struct FchlK {
     int nb, A, nel, nRs2, nRs3, repsize, pbc;
@@ -26,17 +26,19 @@ struct FchlK {
 };
 
 // ---- shared-memory carve-up ----------------------------------------------------------------------------------
-// block : x[A] y[A] z[A] et[A] | Rs2[nRs2] logRs2[nRs2] invRs2[nRs2] Rs3[nRs3] | cell[9] icell[9] (+pad)
+// block : x[A] y[A] z[A] et[A] | Rs2[nRs2] logRs2[nRs2] invRs2[nRs2] Rs3[nRs3] | cell[9] icell[9] | logRs2_lo[nRs2] (+pad)
+// ln Rs2 and mu are kept as float pairs (hi + lo): the log-normal exponent (ln Rs2 - mu)^2 / (2 sigma^2) amplifies
+// the rounding of its argument by up to 1/sigma^2 ~ 100, which would otherwise cost a digit of the representation.
 // warp  : NB_FIELDS arrays of A entries | row[repsize] | (backward) force[3A]
-constexpr int NB_FIELDS = 14;
-enum { F_IDX = 0, F_DX, F_DY, F_DZ, F_R, F_FC, F_DFC, F_ET, F_MU, F_I2S, F_PREF, F_C0, F_C1, F_C2 };
+constexpr int NB_FIELDS = 15;
+enum { F_IDX = 0, F_DX, F_DY, F_DZ, F_R, F_FC, F_DFC, F_ET, F_MU, F_MULO, F_I2S, F_PREF, F_C0, F_C1, F_C2 };
 
 __host__ __device__ inline int align4(int v) { return (v + 3) & ~3; }
 
 struct Layout {
     int block_floats, warp_floats, off_row, off_force;
     __host__ __device__ Layout(int A, int nRs2, int nRs3, int repsize, bool backward) {
-        block_floats = align4(4 * A + 3 * nRs2 + nRs3 + 18);
+        block_floats = align4(4 * A + 4 * nRs2 + nRs3 + 18);
         off_row = align4(NB_FIELDS * A);
         off_force = off_row + align4(repsize);
         warp_floats = off_force + (backward ? align4(3 * A) : 0);
@@ -87,7 +89,9 @@ __device__ int stage_molecule(const float *X, const float *Z, const int *counts,
     for (int z = threadIdx.x; z < K.nRs2; z += blockDim.x) {
         float r = Rs2[z];
         sRs2[z] = r;
-        sLog2[z] = (float)log((double)r);
+        const double lg = log((double)r);
+        sLog2[z] = (float)lg;
+        scell[18 + z] = (float)(lg - (double)(float)lg);
         sInv2[z] = 1.0f / r;
     }
     for (int z = threadIdx.x; z < K.nRs3; z += blockDim.x) sRs3[z] = Rs3[z];
@@ -126,8 +130,8 @@ __device__ int build_neighbours(const float *sm, float *ws, const FchlK &K, int 
         const unsigned m = __ballot_sync(QMLB_FULL_MASK, ok);
         if (ok) {
             const int pos = nn + __popc(m & ((1u << lane) - 1u));
-            const float r = sqrtf(r2);
-            const double rd = (double)r;
+            const double rd = sqrt((double)dx * dx + (double)dy * dy + (double)dz * dz);
+            const float r = (float)rd;
             const double pi = 3.14159265358979323846;
             const double arg = rd * pi / (double)K.rcut;
             const double fc = 0.5 * (cos(arg) + 1.0);
@@ -147,6 +151,7 @@ __device__ int build_neighbours(const float *sm, float *ws, const FchlK &K, int 
             ws[F_FC * A + pos] = (float)fc;
             ws[F_DFC * A + pos] = (float)dfc;
             ws[F_MU * A + pos] = (float)mu;
+            ws[F_MULO * A + pos] = (float)(mu - (double)(float)mu);
             ws[F_I2S * A + pos] = (float)(0.5 / s2);
             ws[F_PREF * A + pos] = (float)(pow(rd, -(double)K.d2) / (sqrt(s2) * 2.5066282746310002));
             ws[F_C0 * A + pos] = (float)(-0.5 * ds2 / s2 - (double)K.d2 / rd);
@@ -233,6 +238,7 @@ fchl_forward_kernel(const float *__restrict__ X, const float *__restrict__ Z, co
     const Layout L(A, K.nRs2, K.nRs3, K.repsize, false);
     const int natoms = stage_molecule(X, Z, counts, species, Rs2, Rs3, cell, icell, K, mol, sm);
     const float *sLog2 = sm + 4 * A + K.nRs2, *sInv2 = sLog2 + K.nRs2, *sRs3 = sInv2 + K.nRs2;
+    const float *sLog2lo = sRs3 + K.nRs3 + 18;
     float *ws = sm + L.block_floats + (size_t)warp * L.warp_floats;
     float *acc = ws + L.off_row;
     const int *n_et = reinterpret_cast<const int *>(ws + F_ET * A);
@@ -252,11 +258,11 @@ fchl_forward_kernel(const float *__restrict__ X, const float *__restrict__ Z, co
 
         // two-body (fchl_cuda_kernel.cu:586-603): lanes over grid points, neighbours serial
         for (int jn = 0; jn < nn; ++jn) {
-            const float mu = ws[F_MU * A + jn], i2s = ws[F_I2S * A + jn];
+            const float mu = ws[F_MU * A + jn], mulo = ws[F_MULO * A + jn], i2s = ws[F_I2S * A + jn];
             const float pref = ws[F_PREF * A + jn] * ws[F_FC * A + jn];
             float *blk = acc + n_et[jn] * K.nRs2;
             for (int z = lane; z < K.nRs2; z += 32) {
-                const float t = sLog2[z] - mu;
+                const float t = (sLog2[z] - mu) + (sLog2lo[z] - mulo);
                 blk[z] += pref * sInv2[z] * expf(-t * t * i2s);
             }
         }
@@ -314,6 +320,7 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
     const Layout L(A, K.nRs2, K.nRs3, K.repsize, true);
     const int natoms = stage_molecule(X, Z, counts, species, Rs2, Rs3, cell, icell, K, mol, sm);
     const float *sLog2 = sm + 4 * A + K.nRs2, *sInv2 = sLog2 + K.nRs2, *sRs3 = sInv2 + K.nRs2;
+    const float *sLog2lo = sRs3 + K.nRs3 + 18;
     float *ws = sm + L.block_floats + (size_t)warp * L.warp_floats;
     float *grow = ws + L.off_row;
     float *force = ws + L.off_force;  // this warp's contribution to d/dr of every atom of the molecule
@@ -337,13 +344,14 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
         for (int j0 = 0; j0 < nn; j0 += 32) {
             const int jn = j0 + lane;
             if (jn < nn) {
-                const float mu = ws[F_MU * A + jn], i2s = ws[F_I2S * A + jn], pref = ws[F_PREF * A + jn];
+                const float mu = ws[F_MU * A + jn], mulo = ws[F_MULO * A + jn], i2s = ws[F_I2S * A + jn];
+                const float pref = ws[F_PREF * A + jn];
                 const float fc = ws[F_FC * A + jn], dfc = ws[F_DFC * A + jn];
                 const float c0 = ws[F_C0 * A + jn], c1 = ws[F_C1 * A + jn], c2 = ws[F_C2 * A + jn];
                 const float *gb = grow + n_et[jn] * K.nRs2;
                 float gr = 0.f;
                 for (int z = 0; z < K.nRs2; ++z) {
-                    const float t = sLog2[z] - mu;
+                    const float t = (sLog2[z] - mu) + (sLog2lo[z] - mulo);
                     const float base = pref * sInv2[z] * expf(-t * t * i2s);
                     gr += gb[z] * base * (fc * (c0 + t * (c1 + t * c2)) + dfc);
                 }
@@ -464,6 +472,7 @@ fchl_jacobian_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
     const Layout L(A, K.nRs2, K.nRs3, K.repsize, false);
     const int natoms = stage_molecule(X, Z, counts, species, Rs2, Rs3, cell, icell, K, mol, sm);
     const float *sLog2 = sm + 4 * A + K.nRs2, *sInv2 = sLog2 + K.nRs2, *sRs3 = sInv2 + K.nRs2;
+    const float *sLog2lo = sRs3 + K.nRs3 + 18;
     float *ws = sm + L.block_floats + (size_t)warp * L.warp_floats;
     float *acc = ws + L.off_row;
     const int *n_et = reinterpret_cast<const int *>(ws + F_ET * A);
@@ -484,7 +493,8 @@ fchl_jacobian_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
         float *Ji = J + (size_t)i * 3 * R;
 
         for (int jn = 0; jn < nn; ++jn) {
-            const float mu = ws[F_MU * A + jn], i2s = ws[F_I2S * A + jn], pref = ws[F_PREF * A + jn];
+            const float mu = ws[F_MU * A + jn], mulo = ws[F_MULO * A + jn], i2s = ws[F_I2S * A + jn];
+            const float pref = ws[F_PREF * A + jn];
             const float fc = ws[F_FC * A + jn], dfc = ws[F_DFC * A + jn];
             const float c0 = ws[F_C0 * A + jn], c1 = ws[F_C1 * A + jn], c2 = ws[F_C2 * A + jn];
             const float inv_r = 1.0f / ws[F_R * A + jn];
@@ -492,7 +502,7 @@ fchl_jacobian_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
             const int col0 = n_et[jn] * K.nRs2;
             float *Jj = J + (size_t)n_idx[jn] * 3 * R;
             for (int z = lane; z < K.nRs2; z += 32) {
-                const float t = sLog2[z] - mu;
+                const float t = (sLog2[z] - mu) + (sLog2lo[z] - mulo);
                 const float base = pref * sInv2[z] * expf(-t * t * i2s);
                 acc[col0 + z] += base * fc;
                 const float dr = base * (fc * (c0 + t * (c1 + t * c2)) + dfc);

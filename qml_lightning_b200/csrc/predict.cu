@@ -1,0 +1,72 @@
+// Whole-batch energy + gradient prediction for the SORF model: the six stages chained on one stream with a
+// caller-provided workspace, no allocation and no host synchronisation.
+//
+// Replaces HadamardFeaturesModel.forward followed by autograd.grad (models/hadamard_features.py:82-123, 157-162):
+//   group atoms by element -> FCHL19 rows -> PCA -> fused SORF energy/gradient -> PCA^T -> FCHL19 VJP + molecule sums.
+#include "common.cuh"
+
+namespace {
+
+inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+struct Workspace {
+    size_t rows_cap;
+    size_t off_row_of_slot, off_slot_of_row, off_group_start, off_scratch, off_rep, off_x, off_gx, off_energy, total;
+    Workspace(int nb, int A, size_t n_atoms_upper, int nel, int repsize, int width) {
+        const size_t slots = (size_t)nb * A;
+        rows_cap = qmlb_rows_capacity(n_atoms_upper < slots ? n_atoms_upper : slots, nel);
+        size_t o = 0;
+        off_row_of_slot = o; o = align256(o + sizeof(int) * slots);
+        off_slot_of_row = o; o = align256(o + sizeof(int) * rows_cap);
+        off_group_start = o; o = align256(o + sizeof(int) * (nel + 1));
+        off_scratch = o;     o = align256(o + qmlb_group_scratch_bytes(nb, nel));
+        off_rep = o;         o = align256(o + sizeof(float) * rows_cap * repsize);
+        off_x = o;           o = align256(o + sizeof(float) * rows_cap * width);
+        off_gx = o;          o = align256(o + sizeof(float) * rows_cap * width);
+        off_energy = o;      o = align256(o + sizeof(float) * rows_cap);
+        total = o;
+    }
+};
+
+}  // namespace
+
+extern "C" size_t qmlb_predict_workspace_bytes(int nb, int A, size_t n_atoms_upper, int nelements, int repsize, int npcas) {
+    if (nb <= 0 || A <= 0 || nelements <= 0 || repsize <= 0 || npcas <= 0) return 0;
+    return Workspace(nb, A, n_atoms_upper, nelements, repsize, npcas).total;
+}
+
+extern "C" int qmlb_sorf_predict(const float *X, const float *Z, const int *atom_counts, int nb, int A,
+                                 const qmlb_fchl_params *p, const float *cell, const float *inv_cell,
+                                 const float *elements, int nelements, const float *reductors, int npcas,
+                                 const void *packed, int S, int T, float sigma, int fast_math, size_t n_atoms_upper,
+                                 void *workspace, size_t workspace_bytes, float *energy, float *grad_X,
+                                 qmlb_stream_t stream) {
+    QMLB_REQUIRE(X && Z && atom_counts && p && elements && reductors && packed && workspace && energy && grad_X,
+                 "qmlb_sorf_predict: null argument");
+    QMLB_REQUIRE(nb >= 0 && A > 0 && nelements > 0 && npcas > 0, "qmlb_sorf_predict: bad sizes");
+    if (nb == 0) return QMLB_OK;
+    const int repsize = qmlb_fchl19_repsize(p->nspecies, p->nRs2, p->nRs3);
+    const Workspace W(nb, A, n_atoms_upper, nelements, repsize, npcas);
+    QMLB_REQUIRE(workspace_bytes >= W.total, "qmlb_sorf_predict: workspace of %zu bytes given, %zu needed", workspace_bytes,
+                 W.total);
+    QMLB_REQUIRE(((uintptr_t)workspace & 255) == 0, "qmlb_sorf_predict: workspace must be 256-byte aligned");
+    char *base = static_cast<char *>(workspace);
+    int *row_of_slot = reinterpret_cast<int *>(base + W.off_row_of_slot);
+    int *slot_of_row = reinterpret_cast<int *>(base + W.off_slot_of_row);
+    int *group_start = reinterpret_cast<int *>(base + W.off_group_start);
+    float *rep = reinterpret_cast<float *>(base + W.off_rep);
+    float *x = reinterpret_cast<float *>(base + W.off_x);
+    float *gx = reinterpret_cast<float *>(base + W.off_gx);
+    float *atom_energy = reinterpret_cast<float *>(base + W.off_energy);
+    int rc;
+    if ((rc = qmlb_group_by_element(Z, atom_counts, elements, nelements, nb, A, row_of_slot, slot_of_row, group_start,
+                                    W.rows_cap, base + W.off_scratch, stream))) return rc;
+    if ((rc = qmlb_fchl19_forward(X, Z, atom_counts, nb, A, p, cell, inv_cell, row_of_slot, rep, stream))) return rc;
+    if ((rc = qmlb_pca_project(rep, reductors, group_start, nelements, W.rows_cap, repsize, npcas, 0, x, stream))) return rc;
+    if ((rc = qmlb_sorf_energy_grad(x, group_start, slot_of_row, nelements, W.rows_cap, npcas, S, T, sigma, packed,
+                                    fast_math, atom_energy, gx, stream))) return rc;
+    // the representation buffer is reused for d(energy)/d(representation)
+    if ((rc = qmlb_pca_project(gx, reductors, group_start, nelements, W.rows_cap, repsize, npcas, 1, rep, stream))) return rc;
+    return qmlb_fchl19_backward(X, Z, atom_counts, nb, A, p, cell, inv_cell, row_of_slot, rep, grad_X, atom_energy, energy,
+                                stream);
+}
