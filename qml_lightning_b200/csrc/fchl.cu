@@ -209,10 +209,15 @@ __device__ __forceinline__ void triplet_geometry(const float *ws, int A, int j, 
     g.cj = vj * inv_a * inv_c;
     g.ck = vk * inv_b * inv_c;
     g.cth = fminf(1.0f, fmaxf(-1.0f, g.ci));
-    g.sth = sqrtf(fmaxf(0.f, 1.0f - g.cth * g.cth));
-    // upstream regularises 1/(r_ij r_ik sin) as 1/sqrt(max(1e-10, r_ij^2 r_ik^2 - vi^2))  (:1578-1579)
+    // sin(theta_i) from the cross product |d_ij x d_ik| = r_ij r_ik sin(theta): unlike sqrt(1 - cos^2) (what
+    // sinf(acosf(c)) amounts to upstream) it does not cancel for nearly collinear triplets, whose d sin/d cos =
+    // -cos/sin is large.  Upstream regularises 1/(r_ij r_ik sin) as 1/sqrt(max(1e-10, r_ij^2 r_ik^2 - vi^2))
+    // (:1578-1579); r_ij^2 r_ik^2 - vi^2 is the squared cross product, so the same floor (1e-5) is applied to it.
+    const float cx = dyj * dzk - dzj * dyk, cy = dzj * dxk - dxj * dzk, cz = dxj * dyk - dyj * dxk;
+    const float sab = sqrtf(cx * cx + cy * cy + cz * cz);
     const float ab = g.a * g.b;
-    g.w = ab * rsqrtf(fmaxf(1e-10f, ab * ab - vi * vi));
+    g.sth = fminf(1.0f, sab / ab);
+    g.w = ab / fmaxf(sab, 1e-5f);
     g.T = 1.0f + 3.0f * g.ci * g.cj * g.ck;
     g.R = powf(g.a * g.b * g.c, -K.d3);
     g.Fij = ws[F_FC * A + j];
