@@ -134,7 +134,21 @@ __device__ __forceinline__ void fwht_flip(float (&u)[16], float *slab, int l, in
     }
 }
 
+// Parameter blocks (one per stack and transform) are stored interleaved: the q-th float4 of lane l sits at float
+// offset (q*L + l)*4, so that one 128-bit load instruction of a vector's L lanes covers L*16 contiguous bytes
+// (4 L1 wavefronts per warp-wide load instead of 16 with a lane-major order).
+template <int L>
 __device__ __forceinline__ void load16(float (&v)[16], const float *p) {
+    const float4 *q = reinterpret_cast<const float4 *>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float4 t = __ldg(q + i * L);
+        v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+    }
+}
+
+// natural (row) order: 16 consecutive floats per lane
+__device__ __forceinline__ void load16_row(float (&v)[16], const float *p) {
     const float4 *q = reinterpret_cast<const float4 *>(p);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -167,19 +181,18 @@ sorf_energy_grad_kernel(const float *__restrict__ x, const int *__restrict__ gro
     while (el + 1 < nel && row >= group_start[el + 1]) ++el;
 
     float xr[16], gx[16];
-    load16(xr, x + (size_t)row * N + l * 16);
+    load16_row(xr, x + (size_t)row * N + l * 16);
 #pragma unroll
     for (int e = 0; e < 16; ++e) gx[e] = 0.f;
     float eacc = 0.f;
 
-    const size_t pos = (size_t)l * 16;
+    const size_t pos = (size_t)l * 4;  // interleaved parameter blocks: float4 index q*L + l
     const float *Dp_e = Dp + (size_t)el * S * T * N;
     const float *bp_e = bp + (size_t)el * S * N;
 
+    // S is the stack count padded to a multiple of V by qmlb_sorf_pack (padding stacks carry zero weights)
     for (int s0 = 0; s0 < S; s0 += C::V) {
-        const int s = s0 + g;
-        const bool valid = s < S;
-        const int sc = valid ? s : S - 1;
+        const int sc = s0 + g;
         const float *Ds = Dp_e + (size_t)sc * T * N + pos;
         float u[16], c[16];
 #pragma unroll
@@ -187,7 +200,7 @@ sorf_energy_grad_kernel(const float *__restrict__ x, const int *__restrict__ gro
         bool in_a = true;
 #pragma unroll
         for (int m = 0; m < T; ++m) {
-            load16(c, Ds + (size_t)m * N);
+            load16<C::L>(c, Ds + (size_t)m * N);
 #pragma unroll
             for (int e = 0; e < 16; ++e) u[e] *= c[e];
             fwht_flip<LOG2N>(u, slab, l, lane, in_a);
@@ -195,25 +208,23 @@ sorf_energy_grad_kernel(const float *__restrict__ x, const int *__restrict__ gro
         }
         {   // features: energy contribution and d/d(arg), in the layout the forward transform ended in
             float a[16];
-            load16(c, bp_e + (size_t)sc * N + pos);
-            load16(a, ap + (size_t)sc * N + pos);
-            const float vf = valid ? 1.0f : 0.0f;
+            load16<C::L>(c, bp_e + (size_t)sc * N + pos);
+            load16<C::L>(a, ap + (size_t)sc * N + pos);
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
                 const float arg = fmaf(u[e], scale, c[e]);
                 float sn, cs;
                 if (FAST) __sincosf(arg, &sn, &cs);
                 else sincosf(arg, &sn, &cs);
-                const float al = a[e] * vf;
-                eacc = fmaf(al, cs, eacc);
-                u[e] = -al * sn;
+                eacc = fmaf(a[e], cs, eacc);
+                u[e] = -a[e] * sn;
             }
         }
 #pragma unroll
         for (int m = T - 1; m >= 0; --m) {
             fwht_flip<LOG2N>(u, slab, l, lane, in_a);
             in_a = !in_a;
-            load16(c, Ds + (size_t)m * N);
+            load16<C::L>(c, Ds + (size_t)m * N);
             if (m > 0) {
 #pragma unroll
                 for (int e = 0; e < 16; ++e) u[e] *= c[e];
@@ -239,34 +250,49 @@ sorf_energy_grad_kernel(const float *__restrict__ x, const int *__restrict__ gro
     if (lane == 0) atom_energy[row] = eacc;
 }
 
+// Source element of packed float index p (0..N-1) of one block: p = (q*L + l)*4 + r holds register e = 4q + r of
+// lane l, i.e. position l*16 + e of layout A, or its layout-B element when `layout_b`.
+__host__ __device__ inline int packed_source(int log2n, int p, bool layout_b) {
+    const int L = 1 << (log2n - 4);
+    const int r = p & 3, l = (p >> 2) % L, q = (p >> 2) / L;
+    const int pos = l * 16 + 4 * q + r;
+    return layout_b ? layoutB_n(log2n, pos) : pos;
+}
+
 __global__ void sorf_pack_kernel(const float *__restrict__ Dmat, const float *__restrict__ bias,
-                                 const float *__restrict__ alpha, int nel, int log2n, int S, int T,
+                                 const float *__restrict__ alpha, int nel, int log2n, int S, int Spad, int T,
                                  float *__restrict__ Dp, float *__restrict__ bp, float *__restrict__ ap) {
     const int N = 1 << log2n;
-    const size_t nD = (size_t)nel * S * T * N, nB = (size_t)nel * S * N, nA = (size_t)S * N;
+    const size_t nD = (size_t)nel * Spad * T * N, nB = (size_t)nel * Spad * N, nA = (size_t)Spad * N;
     const float normf = sqrtf(2.0f / (float)((size_t)S * N));
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nD + nB + nA; i += (size_t)gridDim.x * blockDim.x) {
-        if (i < nD) {  // Dp[el][s][m][pos] <- Dmat[el][m][s][n]
+        if (i < nD) {  // Dp[el][s][m][p] <- Dmat[el][m][s][n]
             const int p = (int)(i % N);
             const int m = (int)((i / N) % T);
-            const int s = (int)((i / ((size_t)N * T)) % S);
-            const int el = (int)(i / ((size_t)N * T * S));
-            const int n = (m & 1) ? layoutB_n(log2n, p) : p;
-            Dp[i] = Dmat[(((size_t)el * T + m) * S + s) * N + n];
+            const int s = (int)((i / ((size_t)N * T)) % Spad);
+            const int el = (int)(i / ((size_t)N * T * Spad));
+            const int n = packed_source(log2n, p, m & 1);
+            Dp[i] = s < S ? Dmat[(((size_t)el * T + m) * S + s) * N + n] : 1.0f;
         } else if (i < nD + nB) {
             const size_t k = i - nD;
             const int p = (int)(k % N);
-            const size_t es = k / N;  // el*S + s
-            const int n = (T & 1) ? layoutB_n(log2n, p) : p;
-            bp[k] = bias[es * N + n];
+            const int s = (int)((k / N) % Spad);
+            const int el = (int)(k / ((size_t)N * Spad));
+            const int n = packed_source(log2n, p, T & 1);
+            bp[k] = s < S ? bias[((size_t)el * S + s) * N + n] : 0.0f;
         } else {
             const size_t k = i - nD - nB;
             const int p = (int)(k % N);
-            const size_t s = k / N;
-            const int n = (T & 1) ? layoutB_n(log2n, p) : p;
-            ap[k] = alpha[s * N + n] * normf;
+            const int s = (int)(k / N);
+            const int n = packed_source(log2n, p, T & 1);
+            ap[k] = s < S ? alpha[(size_t)s * N + n] * normf : 0.0f;  // padding stacks contribute nothing
         }
     }
+}
+
+inline int padded_stacks(int N, int S) {
+    const int V = 512 / N;  // stacks per warp: 32 lanes / (N/16 lanes per vector)
+    return (S + V - 1) / V * V;
 }
 
 int ilog2_exact(int n) {
@@ -297,7 +323,9 @@ int launch_fused(const float *x, const int *group_start, const int *slot_of_row,
 }  // namespace
 
 extern "C" size_t qmlb_sorf_pack_bytes(int nelements, int N, int S, int T) {
-    return sizeof(float) * ((size_t)nelements * S * T * N + (size_t)nelements * S * N + (size_t)S * N);
+    if (N < 16 || N > 512) return 0;
+    const size_t Sp = padded_stacks(N, S);
+    return sizeof(float) * ((size_t)nelements * Sp * T * N + (size_t)nelements * Sp * N + Sp * N);
 }
 
 extern "C" int qmlb_sorf_pack(const float *Dmat, const float *bias, const float *alpha, int nelements, int N, int S,
@@ -306,10 +334,11 @@ extern "C" int qmlb_sorf_pack(const float *Dmat, const float *bias, const float 
     const int log2n = ilog2_exact(N);
     QMLB_REQUIRE(log2n >= 4 && log2n <= 9, "qmlb_sorf_pack: npcas must be a power of two in [16, 512], got %d", N);
     QMLB_REQUIRE(nelements > 0 && S > 0 && T > 0, "qmlb_sorf_pack: bad sizes");
+    const size_t Sp = padded_stacks(N, S);
     float *Dp = static_cast<float *>(packed);
-    float *bp = Dp + (size_t)nelements * S * T * N;
-    float *ap = bp + (size_t)nelements * S * N;
-    sorf_pack_kernel<<<592, 256, 0, qmlb::as_stream(stream)>>>(Dmat, bias, alpha, nelements, log2n, S, T, Dp, bp, ap);
+    float *bp = Dp + (size_t)nelements * Sp * T * N;
+    float *ap = bp + (size_t)nelements * Sp * N;
+    sorf_pack_kernel<<<592, 256, 0, qmlb::as_stream(stream)>>>(Dmat, bias, alpha, nelements, log2n, S, (int)Sp, T, Dp, bp, ap);
     return qmlb::check_launch("qmlb_sorf_pack");
 }
 
@@ -321,18 +350,19 @@ extern "C" int qmlb_sorf_energy_grad(const float *x, const int *group_start, con
     QMLB_REQUIRE(log2n >= 4 && log2n <= 9, "qmlb_sorf_energy_grad: npcas must be a power of two in [16, 512], got %d", N);
     QMLB_REQUIRE(nelements > 0 && S > 0 && T > 0 && sigma > 0.f, "qmlb_sorf_energy_grad: bad sizes");
     if (rows_cap == 0) return QMLB_OK;
+    const size_t Sp = padded_stacks(N, S);
     const float *Dp = static_cast<const float *>(packed);
-    const float *bp = Dp + (size_t)nelements * S * T * N;
-    const float *ap = bp + (size_t)nelements * S * N;
+    const float *bp = Dp + (size_t)nelements * Sp * T * N;
+    const float *ap = bp + (size_t)nelements * Sp * N;
     // coeff_normalisation sqrt(N)/sigma (models/hadamard_features.py:93) times N^(-1/2) per transform
     const float scale = (float)(sqrt((double)N) / (double)sigma * pow((double)N, -0.5 * (double)T));
     cudaStream_t st = qmlb::as_stream(stream);
     switch (log2n) {
-        case 4: return launch_fused<4>(x, group_start, slot_of_row, nelements, rows_cap, S, T, scale, Dp, bp, ap, fast_math, atom_energy, grad_x, st);
-        case 5: return launch_fused<5>(x, group_start, slot_of_row, nelements, rows_cap, S, T, scale, Dp, bp, ap, fast_math, atom_energy, grad_x, st);
-        case 6: return launch_fused<6>(x, group_start, slot_of_row, nelements, rows_cap, S, T, scale, Dp, bp, ap, fast_math, atom_energy, grad_x, st);
-        case 7: return launch_fused<7>(x, group_start, slot_of_row, nelements, rows_cap, S, T, scale, Dp, bp, ap, fast_math, atom_energy, grad_x, st);
-        case 8: return launch_fused<8>(x, group_start, slot_of_row, nelements, rows_cap, S, T, scale, Dp, bp, ap, fast_math, atom_energy, grad_x, st);
-        default: return launch_fused<9>(x, group_start, slot_of_row, nelements, rows_cap, S, T, scale, Dp, bp, ap, fast_math, atom_energy, grad_x, st);
+        case 4: return launch_fused<4>(x, group_start, slot_of_row, nelements, rows_cap, (int)Sp, T, scale, Dp, bp, ap, fast_math, atom_energy, grad_x, st);
+        case 5: return launch_fused<5>(x, group_start, slot_of_row, nelements, rows_cap, (int)Sp, T, scale, Dp, bp, ap, fast_math, atom_energy, grad_x, st);
+        case 6: return launch_fused<6>(x, group_start, slot_of_row, nelements, rows_cap, (int)Sp, T, scale, Dp, bp, ap, fast_math, atom_energy, grad_x, st);
+        case 7: return launch_fused<7>(x, group_start, slot_of_row, nelements, rows_cap, (int)Sp, T, scale, Dp, bp, ap, fast_math, atom_energy, grad_x, st);
+        case 8: return launch_fused<8>(x, group_start, slot_of_row, nelements, rows_cap, (int)Sp, T, scale, Dp, bp, ap, fast_math, atom_energy, grad_x, st);
+        default: return launch_fused<9>(x, group_start, slot_of_row, nelements, rows_cap, (int)Sp, T, scale, Dp, bp, ap, fast_math, atom_energy, grad_x, st);
     }
 }
