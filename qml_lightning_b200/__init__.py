@@ -4,7 +4,7 @@ Public classes keep the upstream names and signatures:
 ``FCHLCuda`` (representations/FCHL.py), ``HadamardFeaturesModel`` (models/hadamard_features.py) and
 ``RandomFourrierFeaturesModel`` (models/random_features.py).  All arithmetic runs in hand-written sm_100a kernels
 behind the C ABI of ``lib/libqmlb200.so``; ``lib/libqmlb200_torch.so`` registers the TorchScript operators.
-Both are built in-tree by ``python -m qml_lightning_b200.build``; nothing falls back to the CPU or to PyTorch ops.
+Both are built in-tree by ``python qml_lightning_b200/build.py``; nothing falls back to the CPU or to PyTorch ops.
 """
 import os
 
@@ -22,7 +22,7 @@ def load_torch_ops():
     global _ops_loaded
     if not _ops_loaded:
         if not os.path.exists(TORCH_OPS_LIB):
-            raise RuntimeError(f"{TORCH_OPS_LIB} not found: build it with `python -m qml_lightning_b200.build`")
+            raise RuntimeError(f"{TORCH_OPS_LIB} not found: build it with `python qml_lightning_b200/build.py`")
         _lib.load()  # libqmlb200.so must be resolvable first
         torch.ops.load_library(TORCH_OPS_LIB)
         _ops_loaded = True

@@ -3,7 +3,8 @@
 ``build_native()`` compiles every ``csrc/*.cu`` into ``qml_lightning_b200/lib/libqmlb200.so`` with nvcc (no torch
 headers, a few seconds per file); ``build_torch_ops()`` compiles the TorchScript operator shim
 ``csrc/torch_ops.cpp`` with g++ against the installed torch and links it to that library.  Objects are cached by
-source modification time.  Run as ``python -m qml_lightning_b200.build``.
+source modification time.  Run as ``python qml_lightning_b200/build.py`` (a plain script, so that it works before the
+libraries exist; importing the package loads them).
 """
 import glob
 import os
