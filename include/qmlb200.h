@@ -126,6 +126,24 @@ int qmlb_group_by_element(const float *Z, const int *atom_counts, const float *e
                           int A, int *row_of_slot, int *slot_of_row, int *group_start, size_t rows_cap,
                           void *scratch, qmlb_stream_t stream);
 
+/* Allocation-free variant of qmlb_group_by_element: identical outputs, but the scratch counters live in a fixed
+ * QMLB_GROUP_STATIC_SCRATCH_BYTES array inside the library instead of caller memory.  It has no counterpart in the
+ * upstream project.  It is meant for callers that receive their buffers from a host application and must not
+ * allocate device memory themselves (a simulation engine's force plug-in working inside the engine's memory
+ * budget; a latency-critical thread that must stay out of cudaMalloc/cudaFree, which serialise against all streams).
+ *  - Limit: qmlb_group_scratch_bytes(nb, nelements) <= QMLB_GROUP_STATIC_SCRATCH_BYTES, i.e. about
+ *    32 * 262,000 / nelements molecules per call; larger batches are rejected with QMLB_ERR_INVALID.
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *    current); make that first call before starting any stream capture.  No call allocates or frees memory.
+ *  - All calls on a device share the one array: calls whose kernels may overlap on the GPU (different streams,
+ *    different host threads) race on it and must be ordered by the caller.  The array keeps the previous call's
+ *    counters; none of them needs clearing because every counter is rewritten before it is read.
+ *  - Every GPU that loads the library carries the array (1 MiB) until the process exits. */
+#define QMLB_GROUP_STATIC_SCRATCH_BYTES (1u << 20)
+int qmlb_group_by_element_noalloc(const float *Z, const int *atom_counts, const float *elements, int nelements, int nb,
+                                  int A, int *row_of_slot, int *slot_of_row, int *group_start, size_t rows_cap,
+                                  qmlb_stream_t stream);
+
 /* ---- PCA projection ----------------------------------------------------------------------- */
 
 /* project_representation = torch.matmul(X, reductor) per element (representations/dimensionality_reduction.py:47-58;

@@ -35,6 +35,7 @@ SIGNATURES = {
     'qmlb_rows_capacity': (c_size_t, [c_size_t, c_int]),
     'qmlb_group_scratch_bytes': (c_size_t, [c_int, c_int]),
     'qmlb_group_by_element': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    'qmlb_group_by_element_noalloc': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     'qmlb_pca_project': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_int, c_int, c_int, c_void_p, c_void_p]),
     'qmlb_sorf_coefficients': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]),
     'qmlb_sorf_coefficients_backward': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]),
@@ -57,7 +58,7 @@ def load():
     global _lib
     if _lib is None:
         if not os.path.exists(LIB_PATH):
-            raise RuntimeError(f"{LIB_PATH} not found: build it with `python -m qml_lightning_b200.build` "
+            raise RuntimeError(f"{LIB_PATH} not found: build it with `python qml_lightning_b200/build.py` "
                                "(there is no CPU or PyTorch fallback)")
         lib = ctypes.CDLL(LIB_PATH)
         for name, (res, args) in SIGNATURES.items():

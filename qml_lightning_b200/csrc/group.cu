@@ -152,3 +152,58 @@ extern "C" int qmlb_group_by_element(const float *Z, const int *atom_counts, con
                                           row_of_slot, slot_of_row, (long)rows_cap);
     return qmlb::check_launch("qmlb_group_by_element");
 }
+
+// ---- allocation-free variant ---------------------------------------------------------------------------------
+// Same grouping, but the per-block counters live in a fixed array inside the library image instead of in memory
+// the caller allocated.  It serves callers that are handed their input and output buffers and may not allocate:
+// a force-field plug-in called back by a simulation engine that owns the whole device-memory budget, or a
+// service thread that must never enter the allocator because cudaMalloc / cudaFree serialise against every
+// stream of the process.
+namespace {
+
+// Held by every GPU that loads the library until the process exits (QMLB_GROUP_STATIC_SCRATCH_BYTES = 1 MiB).
+static __device__ __align__(256) unsigned char g_group_scratch[QMLB_GROUP_STATIC_SCRATCH_BYTES];
+
+constexpr int MAX_DEVICES = 64;
+void *g_group_scratch_addr[MAX_DEVICES] = {};  // device address of the array, per device ordinal
+
+// In host code `g_group_scratch` is only a handle of the symbol, not an address a kernel could use: the device
+// address has to be looked up, with the device current, through cudaGetSymbolAddress.  Done once per device.
+int static_scratch_address(void **out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+        qmlb::set_error("qmlb_group_by_element_noalloc: cudaGetDevice: %s (device %d)", cudaGetErrorString(e), dev);
+        return QMLB_ERR_CUDA;
+    }
+    void *p = __atomic_load_n(&g_group_scratch_addr[dev], __ATOMIC_ACQUIRE);
+    if (p == nullptr) {
+        e = cudaGetSymbolAddress(&p, g_group_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            qmlb::set_error("qmlb_group_by_element_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            return QMLB_ERR_CUDA;
+        }
+        __atomic_store_n(&g_group_scratch_addr[dev], p, __ATOMIC_RELEASE);  // every thread would store the same value
+    }
+    *out = p;
+    return QMLB_OK;
+}
+
+}  // namespace
+
+extern "C" int qmlb_group_by_element_noalloc(const float *Z, const int *atom_counts, const float *elements,
+                                             int nelements, int nb, int A, int *row_of_slot, int *slot_of_row,
+                                             int *group_start, size_t rows_cap, qmlb_stream_t stream) {
+    QMLB_REQUIRE(nb > 0 && nelements > 0, "qmlb_group_by_element_noalloc: bad batch shape");
+    const size_t need = qmlb_group_scratch_bytes(nb, nelements);
+    QMLB_REQUIRE(need <= (size_t)QMLB_GROUP_STATIC_SCRATCH_BYTES,
+                 "qmlb_group_by_element_noalloc: nb=%d molecules with %d elements need %zu bytes of scratch, the built-in "
+                 "array holds %u; split the batch or use qmlb_group_by_element with caller-owned scratch",
+                 nb, nelements, need, (unsigned)QMLB_GROUP_STATIC_SCRATCH_BYTES);
+    void *scratch = nullptr;
+    if (int rc = static_scratch_address(&scratch)) return rc;
+    // Nothing in the array has to start at zero: the counting kernel overwrites every counter that the scan and
+    // the assignment read, so contents left by an earlier call are never observed.
+    return qmlb_group_by_element(Z, atom_counts, elements, nelements, nb, A, row_of_slot, slot_of_row, group_start,
+                                 rows_cap, scratch, stream);
+}
