@@ -66,7 +66,7 @@ class BaseKernel():
         max_atoms = int(counts.max()) if zbatch else 0
         total = int(counts.sum())
         mol_ids = np.repeat(np.arange(zbatch, dtype=np.int32), counts)
-        starts = np.concatenate(([0], np.cumsum(counts)[:-1])).astype(np.int64)
+        starts = (np.cumsum(counts) - counts).astype(np.int64)
         atom_ids = (np.arange(total, dtype=np.int64) - np.repeat(starts, counts)).astype(np.int32)
         coords = np.zeros((zbatch, max_atoms, 3), dtype=np.float32)
         charges = np.zeros((zbatch, max_atoms), dtype=np.float32)

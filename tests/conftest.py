@@ -1,4 +1,6 @@
+import importlib.util
 import os
+import shutil
 import sys
 
 import pytest
@@ -12,6 +14,20 @@ UPSTREAM = os.environ.get('QML_LIGHTNING_UPSTREAM', '/root/reference')
 
 def pytest_configure(config):
     config.addinivalue_line('markers', 'gpu: needs a CUDA device (run on the B200 box)')
+
+
+def _ensure_built():
+    """Build the shared libraries when a compiler is at hand and they are missing or stale (cached by mtime)."""
+    if shutil.which('nvcc') is None and not os.path.exists('/usr/local/cuda/bin/nvcc'):
+        return
+    spec = importlib.util.spec_from_file_location('qmlb200_build', os.path.join(ROOT, 'qml_lightning_b200', 'build.py'))
+    b = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(b)
+    b.build_native(verbose=False)
+    b.build_torch_ops(verbose=False)
+
+
+_ensure_built()
 
 
 @pytest.fixture(scope='session')

@@ -1,0 +1,193 @@
+"""GPU tests of the reference-facing surfaces: Python model classes, TorchScript operators, golden vectors."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+DEV = 'cuda:0'
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def build_model(X, Z, c, species, npcas, nstacks, T=1, seed=7):
+    import qml_lightning_b200 as q
+    p = H.fchl_params(species)
+    ref = H.sorf_model(X, Z, c, p, species, npcas, nstacks, T, seed=seed)
+    rep = q.FCHLCuda(species=np.array(species), rcut=p.rcut, nRs2=p.nRs2, nRs3=p.nRs3, eta2=p.eta2, eta3=p.eta3,
+                     two_body_decay=p.two_body_decay, three_body_weight=p.three_body_weight,
+                     three_body_decay=p.three_body_decay, device=DEV)
+    m = q.HadamardFeaturesModel(rep=rep, elements=np.array(species), ntransforms=T, sigma=ref['sigma'], npcas=npcas,
+                                nstacks=nstacks)
+    m.reductors = ref['reductors'].to(DEV)
+    m.Dmat = ref['Dmat'].to(DEV)
+    m.bias = ref['bias'].to(DEV)
+    m.set_alpha(ref['alpha'].to(DEV))
+    return p, ref, m
+
+
+def ids(c, A):
+    counts = c.tolist()
+    atom = torch.cat([torch.arange(n, dtype=torch.int32) for n in counts])
+    mol = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, n in enumerate(counts)])
+    return atom.to(DEV), mol.to(DEV)
+
+
+@pytest.mark.parametrize('name', ['c0', 'mixed'])
+def test_golden_vectors_on_gpu(name):
+    """CUDA path against the committed oracle vectors (tests/golden/make_golden.py)."""
+    from qml_lightning_b200 import cabi
+    g = np.load(os.path.join(ROOT, 'tests', 'golden', 'sorf_small.npz'))
+    X, Z, c = (torch.from_numpy(g[f'{name}_{k}']) for k in ('X', 'Z', 'counts'))
+    species = g[f'{name}_species'].tolist()
+    p = H.fchl_params(species)
+    kp = H.kernel_params(p, DEV)
+    rep = cabi.fchl19_forward(X.to(DEV), Z.to(DEV), c.to(DEV), kp).cpu().double().numpy()
+    assert np.abs(rep - g[f'{name}_rep']).max() <= 2e-6 * np.abs(g[f'{name}_rep']).max()
+    packed = cabi.sorf_pack(*(torch.from_numpy(g[f'{name}_{k}']).to(DEV) for k in ('Dmat', 'bias', 'alpha')))
+    E, gX = cabi.sorf_predict(X.to(DEV), Z.to(DEV), c.to(DEV), kp, torch.tensor(species, dtype=torch.float32, device=DEV),
+                              torch.from_numpy(g[f'{name}_reductors']).to(DEV), packed, int(g[f'{name}_nstacks']),
+                              int(g[f'{name}_ntransforms']), float(g[f'{name}_sigma']))
+    E_ref = torch.from_numpy(g[f'{name}_E'])
+    assert ((E.cpu().double() - E_ref).abs() <= H.energy_tolerance(E_ref)).all()
+    assert np.abs(-gX.cpu().double().numpy() - g[f'{name}_F']).max() <= 1e-4
+
+
+def test_model_forward_autograd_and_predict_opt():
+    from oracle import energy_and_forces
+    X, Z, c, species = H.batch_mixed(20, seed=31)
+    p, ref, m = build_model(X, Z, c, species, 64, 16)
+    E_ref, F_ref = energy_and_forces(X, Z, c, p, ref)
+    Xd = X.to(DEV).requires_grad_(True)
+    atomIDs, molIDs = ids(c, X.shape[1])
+    E = m.forward(Xd, Z.to(DEV), atomIDs, molIDs, c.to(DEV))
+    F, = torch.autograd.grad(-E.sum(), Xd)                      # the upstream usage (README.md:58-75)
+    assert ((E.detach().cpu().double() - E_ref).abs() <= H.energy_tolerance(E_ref)).all()
+    assert (F.cpu().double() - F_ref).abs().max() <= 1e-4
+    E2, F2 = m.predict_opt(X.to(DEV), Z.to(DEV), atomIDs, molIDs, c.to(DEV))
+    assert torch.equal(E2, E.detach()) and (F2 - F).abs().max() <= 1e-5
+    # weighting the energies scales the gradient per molecule (backward of the fused operator)
+    w = torch.linspace(0.5, 1.5, X.shape[0], device=DEV)
+    Xd2 = X.to(DEV).requires_grad_(True)
+    g, = torch.autograd.grad((m.forward(Xd2, Z.to(DEV), atomIDs, molIDs, c.to(DEV)) * w).sum(), Xd2)
+    assert (g + F * w[:, None, None]).abs().max() <= 1e-5
+    # list-of-arrays entry point
+    Xl = [X[i, :int(c[i])].numpy() for i in range(X.shape[0])]
+    Zl = [Z[i, :int(c[i])].numpy() for i in range(X.shape[0])]
+    m.nbatch_test = 7
+    E3, F3 = m.predict(Xl, Zl, X.shape[1], forces=True)
+    assert ((E3.cpu().double() - E_ref).abs() <= H.energy_tolerance(E_ref)).all()
+    assert (F3.cpu().double() - F_ref).abs().max() <= 1e-4
+
+
+def test_unfused_operator_chain_matches_fused_forward():
+    """The fine-grained operators that saved upstream models call give the same energies and forces."""
+    X, Z, c, species = H.batch_c0(12, seed=8)
+    p, ref, m = build_model(X, Z, c, species, 128, 8)
+    atomIDs, molIDs = ids(c, X.shape[1])
+    Xa = X.to(DEV).requires_grad_(True)
+    Ea = m.forward(Xa, Z.to(DEV), atomIDs, molIDs, c.to(DEV))
+    Fa, = torch.autograd.grad(-Ea.sum(), Xa)
+    Xb = X.to(DEV).requires_grad_(True)
+    Eb = m.forward_unfused(Xb, Z.to(DEV), atomIDs, molIDs, c.to(DEV))
+    Fb, = torch.autograd.grad(-Eb.sum(), Xb)
+    assert (Ea - Eb).abs().max() <= 1e-5 * max(1.0, float(Ea.abs().max()))
+    assert (Fa - Fb).abs().max() <= 1e-4
+
+
+class UpstreamStyleModule(torch.nn.Module):
+    """Calls the operators the way a model scripted by the upstream project does: all arguments are tensors,
+    scalars are 0-dim CPU tensors (upstream cuda/torchscript/FCHL19.cpp:318-327, SORF.cpp:138-149)."""
+
+    def __init__(self, m):
+        super().__init__()
+        r = m.rep
+        self.species, self.Rs2, self.Rs3 = r.species, r.Rs2, r.Rs3
+        self.eta2, self.eta3, self.d2, self.w3, self.d3, self.rcut = (r.eta2, r.eta3, r.two_body_decay,
+                                                                       r.three_body_weight, r.three_body_decay, r.rcut)
+        self.reductors, self.Dmat, self.bias, self.alpha = m.reductors, m.Dmat, m.bias, m.alpha
+        self.elements = m.elements
+        self.norm = torch.sqrt(torch.tensor(float(m.npcas))) / m.sigma
+        self.ntransforms = m.ntransforms
+        self.nfeat = m.nfeatures()
+
+    def forward(self, X, Z, atomIDs, molIDs, atom_counts):
+        cell = torch.empty(0, 3, 3, device=X.device)
+        rep = torch.ops.qml_lightning_fchl.fchl_forwards(X, Z, self.species, atomIDs, molIDs, atom_counts, cell, cell,
+                                                         self.Rs2, self.Rs3, self.eta2, self.eta3, self.d2, self.w3,
+                                                         self.d3, self.rcut)
+        feats = torch.zeros(X.shape[0], self.nfeat, device=X.device, dtype=torch.float32)
+        for i in range(self.elements.shape[0]):
+            mask = Z.int() == self.elements[i]
+            idx = torch.where(mask)[0].type(torch.int)
+            sub = rep[mask]
+            if sub.shape[0] == 0:
+                continue
+            sub = torch.matmul(sub, self.reductors[i])
+            co = torch.ops.qml_lightning_sorf.get_SORF_coefficients(sub, self.Dmat[i], self.norm, self.ntransforms)
+            co = co.view(co.shape[0], co.shape[1] * co.shape[2])
+            feats += torch.ops.qml_lightning_sorf.get_cos_features(co, self.bias[i], torch.tensor(X.shape[0]), idx)
+        return torch.matmul(feats, self.alpha.float())
+
+
+def test_scripted_archives_round_trip(tmp_path):
+    """save_jit_model / torch.jit.load for the fused forward and for an upstream-style operator graph."""
+    X, Z, c, species = H.batch_c0(5, seed=9)
+    p, ref, m = build_model(X, Z, c, species, 32, 8, T=2)
+    atomIDs, molIDs = ids(c, X.shape[1])
+    args = (Z.to(DEV), atomIDs, molIDs, c.to(DEV))
+    E = m.forward(X.to(DEV), *args)
+    path = str(tmp_path / 'model_sorf.pt')
+    m.save_jit_model(path)
+    loaded = torch.jit.load(path)
+    Xl = X.to(DEV).requires_grad_(True)
+    El = loaded.forward(Xl, *args)
+    Fl, = torch.autograd.grad(-El.sum(), Xl)
+    assert torch.equal(El.detach(), E)
+    legacy = torch.jit.script(UpstreamStyleModule(m))
+    lpath = str(tmp_path / 'legacy.pt')
+    legacy.save(lpath)
+    legacy = torch.jit.load(lpath)
+    Xg = X.to(DEV).requires_grad_(True)
+    Eg = legacy.forward(Xg, *args)
+    Fg, = torch.autograd.grad(-Eg.sum(), Xg)
+    assert (Eg - E).abs().max() <= 1e-5 * max(1.0, float(E.abs().max()))
+    assert (Fg - Fl).abs().max() <= 1e-4
+
+
+def test_fchlcuda_methods():
+    import qml_lightning_b200 as q
+    X, Z, c, species = H.batch_mixed(6, seed=3, max_atoms=10)
+    rep = q.FCHLCuda(species=np.array(species), nRs2=8, nRs3=6, device=DEV)
+    Xd, Zd, cd = X.to(DEV), Z.to(DEV), c.to(DEV)
+    atomIDs, molIDs = ids(c, X.shape[1])
+    r = rep.get_representation(Xd, Zd, atomIDs, molIDs, cd)
+    r2, jac = rep.get_representation_and_derivative(Xd, Zd, atomIDs, molIDs, cd)
+    assert torch.allclose(r, r2, rtol=1e-6, atol=1e-7)
+    fd = rep.rep_deriv_fd(Xd, Zd, atomIDs, molIDs, cd, dx=0.002)        # [nb, i, a, x, c]
+    assert (jac.double() - fd).abs().max() <= 2e-3 * max(1.0, float(fd.abs().max()))
+    nn = rep.get_neighbours(Xd, Zd, cd)
+    nl = rep.get_neighbourlist(Xd, Zd, int(nn.max()), cd)
+    assert nn.shape == (6, int(c.max())) and nl.shape == (6, int(c.max()), int(nn.max()))
+    et = rep.get_element_types(Xd, Zd, cd)
+    assert int(et.max()) < len(species)
+    rf = rep.forward(Xd, Zd, atomIDs, molIDs, cd)                        # operator path
+    assert torch.allclose(rf, r, rtol=1e-6, atol=1e-7)
+
+
+def test_upstream_known_answer_through_cuda(upstream_dir):
+    """Upstream's own fixture and script literals through the CUDA operators (only where an upstream checkout exists)."""
+    from tests.test_oracle_kat import load_kat
+    from qml_lightning_b200 import cabi
+    t, u, p, model, X, Z, counts = load_kat(upstream_dir)
+    kp = H.kernel_params(p, DEV)
+    packed = cabi.sorf_pack(model['Dmat'].to(DEV), model['bias'].to(DEV), model['alpha'].float().to(DEV))
+    E, gX = cabi.sorf_predict(X.to(DEV), Z.to(DEV), counts.to(DEV), kp,
+                              torch.tensor(model['elements'], dtype=torch.float32, device=DEV), model['reductors'].to(DEV),
+                              packed, 128, 1, model['sigma'])
+    total = float(E.cpu()) + t['self_energy'][Z.long()].sum().item()
+    assert np.isclose(u['ref_energy'], total)
+    assert np.isclose(u['ref_forces'], -gX[0].cpu().numpy(), rtol=1e-4, atol=5e-4).all()
