@@ -231,16 +231,22 @@ def main():
     repbuf = torch.empty(g.rows_cap, rep.get_repsize(), dtype=torch.float32, device=dev)
     cabi.fchl19_forward(Xd, Zd, cd, kp, row_of_slot=g.row_of_slot, out=repbuf)
     xproj = cabi.pca_project(repbuf, model.reductors, g)
+    def sorf_alone():
+        cabi.sorf_energy_grad(xproj, g, model.packed, NPCAS, NSTACKS, 1, SIGMA, model.fast_math)
+
+    for _ in range(3):          # warm-up: also lets the caching allocator keep the output blocks
+        sorf_alone()
+    torch.cuda.synchronize()
     kev = []
-    for _ in range(max(3, min(args.steps, 10))):
+    for _ in range(max(5, min(args.steps, 20))):
         flush.fill_(1)
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
-        cabi.sorf_energy_grad(xproj, g, model.packed, NPCAS, NSTACKS, 1, SIGMA, model.fast_math)
+        sorf_alone()
         e.record()
         kev.append((s, e))
     torch.cuda.synchronize()
-    k_ms = float(np.mean([s.elapsed_time(e) for s, e in kev]))
+    k_ms = float(np.median([s.elapsed_time(e) for s, e in kev]))
 
     # ---- end to end through the public API: pinned host -> device -> predict_opt -> host ----------------------------
     hX, hZ, hc = (torch.from_numpy(a).pin_memory() for a in (X, Z, counts))
@@ -314,8 +320,8 @@ def main():
 
 # DRAM bytes per atom of the fused SORF kernel from the ncu capture summarised in
 # profiles/sorf_energy_grad_kernel_c1.md (dram__bytes_read.sum + dram__bytes_write.sum divided by the atoms of the
-# captured launch); None until a capture exists.
-SORF_KERNEL_DRAM_BYTES_PER_ATOM = None
+# captured launch: 218.9 MB read + 175.6 MB written for 210,000 atoms).
+SORF_KERNEL_DRAM_BYTES_PER_ATOM = 1879
 
 if __name__ == '__main__':
     main()
