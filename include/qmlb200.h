@@ -212,6 +212,25 @@ int qmlb_sorf_predict(const float *X, const float *Z, const int *atom_counts, in
                       size_t n_atoms_upper, void *workspace, size_t workspace_bytes, float *energy, float *grad_X,
                       qmlb_stream_t stream);
 
+/* ---- RFF ------------------------------------------------------------------------------------ */
+
+/* Fused replacement of the RFF model's feature stage and its autograd backward
+ * (models/random_features.py:98-100: index_add_ of sqrt(2/D) cos(x @ W_e + b_e), then matmul with alpha): per row a
+ *   atom_energy[a] = sum_f alpha_f sqrt(2/D) cos((x_a W_e)_f + b_ef),   grad_x[a,:] = d atom_energy[a] / d x_a
+ * x f32[rows_cap, npcas] element-grouped, W f32[nelements, npcas, D], b f32[nelements, D], alpha f32[D].
+ * npcas in {32, 64, 128, 256}. */
+int qmlb_rff_energy_grad(const float *x, const int *group_start, const int *slot_of_row, int nelements, size_t rows_cap,
+                         int npcas, int nfeatures, const float *W, const float *b, const float *alpha, int fast_math,
+                         float *atom_energy, float *grad_x, qmlb_stream_t stream);
+
+/* RandomFourrierFeaturesModel.forward + autograd.grad (models/random_features.py:69-102, 104-158) as one call;
+ * same conventions and workspace as qmlb_sorf_predict. */
+int qmlb_rff_predict(const float *X, const float *Z, const int *atom_counts, int nb, int A, const qmlb_fchl_params *p,
+                     const float *cell, const float *inv_cell, const float *elements, int nelements,
+                     const float *reductors, int npcas, const float *W, const float *b, const float *alpha, int nfeatures,
+                     int fast_math, size_t n_atoms_upper, void *workspace, size_t workspace_bytes, float *energy,
+                     float *grad_X, qmlb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

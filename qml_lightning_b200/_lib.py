@@ -48,6 +48,11 @@ SIGNATURES = {
     'qmlb_sorf_predict': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, P, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                   c_int, c_void_p, c_int, c_int, c_float, c_int, c_size_t, c_void_p, c_size_t, c_void_p,
                                   c_void_p, c_void_p]),
+    'qmlb_rff_energy_grad': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                     c_int, c_void_p, c_void_p, c_void_p]),
+    'qmlb_rff_predict': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, P, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                 c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_size_t, c_void_p, c_size_t, c_void_p,
+                                 c_void_p, c_void_p]),
 }
 
 _lib = None

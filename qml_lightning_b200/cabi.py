@@ -303,3 +303,42 @@ def sorf_predict(X, Z, atom_counts, fchl, elements, reductors, packed, S, T, sig
                                 float(sigma), int(bool(fast_math)), upper, _p(ws), ws.numel(), _p(energy), _p(grad_X),
                                 _stream(X.device)), 'qmlb_sorf_predict')
     return energy, grad_X
+
+
+def rff_energy_grad(x, grouping, W, b, alpha, fast_math=True):
+    """Per-row energies and gradients of the RFF feature stage (``qmlb_rff_energy_grad``)."""
+    nel, K, D = W.shape
+    rows = grouping.rows_cap
+    atom_energy = torch.empty(rows, dtype=torch.float32, device=x.device)
+    grad_x = torch.empty(rows, K, dtype=torch.float32, device=x.device)
+    check(_lib.load().qmlb_rff_energy_grad(_p(x, torch.float32, 'x'), _p(grouping.group_start), _p(grouping.slot_of_row), nel,
+                                           rows, K, D, _p(W.contiguous(), torch.float32, 'W'),
+                                           _p(b.contiguous(), torch.float32, 'b'), _p(alpha.contiguous(), torch.float32, 'alpha'),
+                                           int(bool(fast_math)), _p(atom_energy), _p(grad_x), _stream(x.device)),
+          'qmlb_rff_energy_grad')
+    return atom_energy, grad_x
+
+
+def rff_predict(X, Z, atom_counts, fchl, elements, reductors, W, b, alpha, cell=None, inv_cell=None, n_atoms_upper=None,
+                fast_math=True, energy=None, grad_X=None):
+    """Energies ``[nb]`` and ``dE/dX [nb,A,3]`` of the RFF model through ``qmlb_rff_predict``."""
+    X, Z, atom_counts, nb, A = _batch(X, Z, atom_counts)
+    cell, inv_cell = _cells(cell, inv_cell)
+    nel, repsize, N = reductors.shape
+    D = W.shape[-1]
+    lib = _lib.load()
+    upper = nb * A if n_atoms_upper is None else int(n_atoms_upper)
+    ws = _workspace(X.device, lib.qmlb_predict_workspace_bytes(nb, A, upper, nel, repsize, N))
+    if energy is None:
+        energy = torch.empty(nb, dtype=torch.float32, device=X.device)
+    if grad_X is None:
+        grad_X = torch.empty(nb, A, 3, dtype=torch.float32, device=X.device)
+    pc = fchl.c()
+    check(lib.qmlb_rff_predict(_p(X, torch.float32, 'coordinates'), _p(Z, torch.float32, 'charges'),
+                               _p(atom_counts, torch.int32, 'atom_counts'), nb, A, ctypes.byref(pc), _p(cell), _p(inv_cell),
+                               _p(elements.contiguous(), torch.float32, 'elements'), nel,
+                               _p(reductors.contiguous(), torch.float32, 'reductors'), N,
+                               _p(W.contiguous(), torch.float32, 'W'), _p(b.contiguous(), torch.float32, 'b'),
+                               _p(alpha.contiguous(), torch.float32, 'alpha'), D, int(bool(fast_math)), upper, _p(ws),
+                               ws.numel(), _p(energy), _p(grad_X), _stream(X.device)), 'qmlb_rff_predict')
+    return energy, grad_X

@@ -35,21 +35,21 @@ extern "C" size_t qmlb_predict_workspace_bytes(int nb, int A, size_t n_atoms_upp
     return Workspace(nb, A, n_atoms_upper, nelements, repsize, npcas).total;
 }
 
-extern "C" int qmlb_sorf_predict(const float *X, const float *Z, const int *atom_counts, int nb, int A,
-                                 const qmlb_fchl_params *p, const float *cell, const float *inv_cell,
-                                 const float *elements, int nelements, const float *reductors, int npcas,
-                                 const void *packed, int S, int T, float sigma, int fast_math, size_t n_atoms_upper,
-                                 void *workspace, size_t workspace_bytes, float *energy, float *grad_X,
-                                 qmlb_stream_t stream) {
-    QMLB_REQUIRE(X && Z && atom_counts && p && elements && reductors && packed && workspace && energy && grad_X,
-                 "qmlb_sorf_predict: null argument");
-    QMLB_REQUIRE(nb >= 0 && A > 0 && nelements > 0 && npcas > 0, "qmlb_sorf_predict: bad sizes");
+namespace {
+
+// Stages shared by the SORF and RFF models; `features` maps projected rows to per-atom energies and gradients.
+template <typename FeatureStage>
+int predict_pipeline(const float *X, const float *Z, const int *atom_counts, int nb, int A, const qmlb_fchl_params *p,
+                     const float *cell, const float *inv_cell, const float *elements, int nelements,
+                     const float *reductors, int npcas, size_t n_atoms_upper, void *workspace, size_t workspace_bytes,
+                     float *energy, float *grad_X, qmlb_stream_t stream, const char *who, FeatureStage features) {
+    QMLB_REQUIRE(X && Z && atom_counts && p && elements && reductors && workspace && energy && grad_X, "%s: null argument", who);
+    QMLB_REQUIRE(nb >= 0 && A > 0 && nelements > 0 && npcas > 0, "%s: bad sizes", who);
     if (nb == 0) return QMLB_OK;
     const int repsize = qmlb_fchl19_repsize(p->nspecies, p->nRs2, p->nRs3);
     const Workspace W(nb, A, n_atoms_upper, nelements, repsize, npcas);
-    QMLB_REQUIRE(workspace_bytes >= W.total, "qmlb_sorf_predict: workspace of %zu bytes given, %zu needed", workspace_bytes,
-                 W.total);
-    QMLB_REQUIRE(((uintptr_t)workspace & 255) == 0, "qmlb_sorf_predict: workspace must be 256-byte aligned");
+    QMLB_REQUIRE(workspace_bytes >= W.total, "%s: workspace of %zu bytes given, %zu needed", who, workspace_bytes, W.total);
+    QMLB_REQUIRE(((uintptr_t)workspace & 255) == 0, "%s: workspace must be 256-byte aligned", who);
     char *base = static_cast<char *>(workspace);
     int *row_of_slot = reinterpret_cast<int *>(base + W.off_row_of_slot);
     int *slot_of_row = reinterpret_cast<int *>(base + W.off_slot_of_row);
@@ -63,10 +63,43 @@ extern "C" int qmlb_sorf_predict(const float *X, const float *Z, const int *atom
                                     W.rows_cap, base + W.off_scratch, stream))) return rc;
     if ((rc = qmlb_fchl19_forward(X, Z, atom_counts, nb, A, p, cell, inv_cell, row_of_slot, rep, stream))) return rc;
     if ((rc = qmlb_pca_project(rep, reductors, group_start, nelements, W.rows_cap, repsize, npcas, 0, x, stream))) return rc;
-    if ((rc = qmlb_sorf_energy_grad(x, group_start, slot_of_row, nelements, W.rows_cap, npcas, S, T, sigma, packed,
-                                    fast_math, atom_energy, gx, stream))) return rc;
+    if ((rc = features(x, group_start, slot_of_row, W.rows_cap, atom_energy, gx))) return rc;
     // the representation buffer is reused for d(energy)/d(representation)
     if ((rc = qmlb_pca_project(gx, reductors, group_start, nelements, W.rows_cap, repsize, npcas, 1, rep, stream))) return rc;
     return qmlb_fchl19_backward(X, Z, atom_counts, nb, A, p, cell, inv_cell, row_of_slot, rep, grad_X, atom_energy, energy,
                                 stream);
+}
+
+}  // namespace
+
+extern "C" int qmlb_sorf_predict(const float *X, const float *Z, const int *atom_counts, int nb, int A,
+                                 const qmlb_fchl_params *p, const float *cell, const float *inv_cell,
+                                 const float *elements, int nelements, const float *reductors, int npcas,
+                                 const void *packed, int S, int T, float sigma, int fast_math, size_t n_atoms_upper,
+                                 void *workspace, size_t workspace_bytes, float *energy, float *grad_X,
+                                 qmlb_stream_t stream) {
+    QMLB_REQUIRE(packed, "qmlb_sorf_predict: null argument");
+    return predict_pipeline(X, Z, atom_counts, nb, A, p, cell, inv_cell, elements, nelements, reductors, npcas,
+                            n_atoms_upper, workspace, workspace_bytes, energy, grad_X, stream, "qmlb_sorf_predict",
+                            [&](const float *x, const int *group_start, const int *slot_of_row, size_t rows_cap,
+                                float *atom_energy, float *gx) {
+                                return qmlb_sorf_energy_grad(x, group_start, slot_of_row, nelements, rows_cap, npcas, S, T,
+                                                             sigma, packed, fast_math, atom_energy, gx, stream);
+                            });
+}
+
+extern "C" int qmlb_rff_predict(const float *X, const float *Z, const int *atom_counts, int nb, int A,
+                                const qmlb_fchl_params *p, const float *cell, const float *inv_cell,
+                                const float *elements, int nelements, const float *reductors, int npcas, const float *W,
+                                const float *b, const float *alpha, int nfeatures, int fast_math, size_t n_atoms_upper,
+                                void *workspace, size_t workspace_bytes, float *energy, float *grad_X,
+                                qmlb_stream_t stream) {
+    QMLB_REQUIRE(W && b && alpha, "qmlb_rff_predict: null argument");
+    return predict_pipeline(X, Z, atom_counts, nb, A, p, cell, inv_cell, elements, nelements, reductors, npcas,
+                            n_atoms_upper, workspace, workspace_bytes, energy, grad_X, stream, "qmlb_rff_predict",
+                            [&](const float *x, const int *group_start, const int *slot_of_row, size_t rows_cap,
+                                float *atom_energy, float *gx) {
+                                return qmlb_rff_energy_grad(x, group_start, slot_of_row, nelements, rows_cap, npcas,
+                                                            nfeatures, W, b, alpha, fast_math, atom_energy, gx, stream);
+                            });
 }

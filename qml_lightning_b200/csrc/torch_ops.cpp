@@ -6,7 +6,8 @@
 //                        get_num_neighbours}                       (upstream cuda/torchscript/FCHL19.cpp:318-333)
 //   qml_lightning_sorf::{get_SORF_coefficients, get_cos_features}   (upstream cuda/torchscript/SORF.cpp:138-150)
 // and one new operator, qml_lightning_b200::sorf_energy, that the rebuilt HadamardFeaturesModel.forward calls: the
-// whole FCHL19 -> PCA -> SORF -> energy chain with the coordinate gradient computed in the same pass.
+// whole FCHL19 -> PCA -> SORF -> energy chain with the coordinate gradient computed in the same pass (and its RFF
+// twin qml_lightning_b200::rff_energy for RandomFourrierFeaturesModel.forward).
 //
 // This file contains no device code: it only allocates tensors, picks the current stream and device, and forwards
 // raw pointers to libqmlb200.so.  Unlike upstream it honours the current CUDA stream and device of the inputs.
@@ -339,6 +340,55 @@ Tensor sorf_energy(const Tensor &X, const Tensor &Z, const Tensor &atom_counts, 
                                packed, nstacks, ntransforms, sigma, n_atoms_upper, fast_math)[0];
 }
 
+// RFF twin of SorfEnergyFn.
+class RffEnergyFn : public torch::autograd::Function<RffEnergyFn> {
+   public:
+    static variable_list forward(AutogradContext *ctx, Tensor X, Tensor Z, Tensor atom_counts, Tensor cell, Tensor inv_cell,
+                                 Tensor species, Tensor Rs2, Tensor Rs3, Tensor fchl_scalars, Tensor elements,
+                                 Tensor reductors, Tensor W, Tensor b, Tensor alpha, int64_t n_atoms_upper, bool fast_math) {
+        Batch bt(X, Z, atom_counts, cell, inv_cell);
+        c10::cuda::CUDAGuard guard(bt.X.device());
+        Tensor sc = fchl_scalars.to(torch::kCPU).to(torch::kFloat64).contiguous();
+        TORCH_CHECK(sc.numel() == 6, "fchl_scalars must hold eta2, eta3, two_body_decay, three_body_weight, three_body_decay, rcut");
+        const double *s = sc.data_ptr<double>();
+        Fchl f(species, Rs2, Rs3, s[0], s[1], s[2], s[3], s[4], s[5], bt.X.device());
+        Tensor el = f32c(elements.to(bt.X.device())), red = f32c(reductors), Wc = f32c(W), bc = f32c(b),
+               ac = f32c(alpha.to(bt.X.device()));
+        TORCH_CHECK(red.dim() == 3 && red.size(0) == el.numel() && red.size(1) == f.repsize(),
+                    "reductors must be [nelements, repsize, npcas]");
+        TORCH_CHECK(Wc.dim() == 3 && Wc.size(0) == el.numel() && Wc.size(1) == red.size(2) && bc.numel() == el.numel() * Wc.size(2) &&
+                        ac.numel() == Wc.size(2), "W must be [nelements, npcas, D], b [nelements, D], alpha [D]");
+        const int nel = (int)el.numel(), npcas = (int)red.size(2), D = (int)Wc.size(2);
+        const size_t upper = n_atoms_upper > 0 ? (size_t)n_atoms_upper : (size_t)bt.nb * bt.A;
+        const size_t bytes = qmlb_predict_workspace_bytes(bt.nb, bt.A, upper, nel, f.repsize(), npcas);
+        Tensor ws = torch::empty({(int64_t)bytes + 256}, bt.X.options().dtype(torch::kUInt8));
+        char *wp = reinterpret_cast<char *>(((uintptr_t)ws.data_ptr<uint8_t>() + 255) & ~(uintptr_t)255);
+        Tensor E = torch::empty({bt.nb}, bt.X.options());
+        Tensor gX = torch::empty({bt.nb, bt.A, 3}, bt.X.options());
+        check(qmlb_rff_predict(bt.X.data_ptr<float>(), bt.Z.data_ptr<float>(), bt.counts.data_ptr<int>(), bt.nb, bt.A, &f.p,
+                               cell_ptr(bt.cell), cell_ptr(bt.inv_cell), el.data_ptr<float>(), nel, red.data_ptr<float>(), npcas,
+                               Wc.data_ptr<float>(), bc.data_ptr<float>(), ac.data_ptr<float>(), D, fast_math ? 1 : 0, upper, wp,
+                               bytes, E.data_ptr<float>(), gX.data_ptr<float>(), current_stream()),
+              "rff_energy");
+        ctx->save_for_backward({gX});
+        return {E};
+    }
+    static variable_list backward(AutogradContext *ctx, variable_list grad_output) {
+        Tensor gX = ctx->get_saved_variables()[0];
+        Tensor g = grad_output[0].to(gX.dtype()).reshape({-1, 1, 1}) * gX;
+        Tensor u;
+        return {g, u, u, u, u, u, u, u, u, u, u, u, u, u, u, u};
+    }
+};
+
+Tensor rff_energy(const Tensor &X, const Tensor &Z, const Tensor &atom_counts, const Tensor &cell, const Tensor &inv_cell,
+                  const Tensor &species, const Tensor &Rs2, const Tensor &Rs3, const Tensor &fchl_scalars,
+                  const Tensor &elements, const Tensor &reductors, const Tensor &W, const Tensor &b, const Tensor &alpha,
+                  int64_t n_atoms_upper, bool fast_math) {
+    return RffEnergyFn::apply(X, Z, atom_counts, cell, inv_cell, species, Rs2, Rs3, fchl_scalars, elements, reductors, W, b,
+                              alpha, n_atoms_upper, fast_math)[0];
+}
+
 }  // namespace
 
 TORCH_LIBRARY(qml_lightning_fchl, m) {
@@ -357,4 +407,5 @@ TORCH_LIBRARY(qml_lightning_sorf, m) {
 TORCH_LIBRARY(qml_lightning_b200, m) {
     m.def("sorf_pack", sorf_pack);
     m.def("sorf_energy", sorf_energy);
+    m.def("rff_energy", rff_energy);
 }

@@ -2,13 +2,14 @@
 import numpy as np
 import torch
 
+from .. import cabi
 from .kernel import BaseKernel
 
 
 class RandomFourrierFeaturesModel(BaseKernel, torch.nn.Module):
 
     def __init__(self, rep=None, elements=np.array([1, 6, 7, 8]), sigma=2.0, llambda=1e-10, nstacks=8192, npcas=128,
-                 nbatch_train=64, nbatch_test=64):
+                 nbatch_train=64, nbatch_test=64, fast_math=True):
         super(RandomFourrierFeaturesModel, self).__init__(rep, npcas, elements, sigma, llambda)
         self.device = rep.device
         self.npcas = npcas
@@ -18,8 +19,9 @@ class RandomFourrierFeaturesModel(BaseKernel, torch.nn.Module):
         self.species = torch.from_numpy(np.asarray(elements)).float().to(self.device)
         self.sample_elemental_basis()
         self.feature_normalisation = np.sqrt(2.0 / self._nfeatures)
-        self.alpha = None
+        self.alpha = torch.zeros(self._nfeatures, device=self.device, dtype=torch.float)
         self.is_trained = False
+        self.fast_math = bool(fast_math)
 
     def sample_elemental_basis(self):
         """W ~ N(0,1)/(2 sigma^2), b ~ U(0, 2 pi) per element (upstream :42-55)."""
@@ -33,3 +35,51 @@ class RandomFourrierFeaturesModel(BaseKernel, torch.nn.Module):
 
     def nfeatures(self):
         return self._nfeatures
+
+    def set_alpha(self, alpha):
+        self.alpha = alpha.to(self.device)
+        self.is_trained = True
+
+    # ---- inference -----------------------------------------------------------------------------------------------
+    def forward(self, X, Z, atomIDs, molIDs, atom_counts, cell=torch.empty(0, 3, 3), inv_cell=torch.empty(0, 3, 3)):
+        """Energies ``[nbatch]`` (no self energies); differentiable with respect to ``X`` (upstream :69-102)."""
+        assert X.is_cuda, "X tensor must reside on GPU"
+        assert Z.device == X.device, "Z tensor must reside on the same GPU as X"
+        assert atom_counts.device == X.device, "atom_counts tensor must reside on the same GPU as X"
+        return torch.ops.qml_lightning_b200.rff_energy(X, Z, atom_counts, cell, inv_cell, self.rep.species, self.rep.Rs2,
+                                                       self.rep.Rs3, self.rep.kernel_scalars, self.species, self.reductors,
+                                                       self.W, self.b, self.alpha, atomIDs.shape[0], self.fast_math)
+
+    def predict_opt(self, coordinates, charges, atomIDs, molIDs, natom_counts, zcells=None, zinv_cells=None, forces=True,
+                    print_info=False, profiler=False):
+        if self.is_trained is False:
+            raise RuntimeError("must train the model first by calling train()!")
+        dev = coordinates.device
+        energies, grad = cabi.rff_predict(coordinates, charges, natom_counts, self.rep.kernel_params(dev), self.species,
+                                          self.reductors, self.W, self.b, self.alpha.float(), zcells, zinv_cells,
+                                          n_atoms_upper=atomIDs.shape[0], fast_math=self.fast_math)
+        if print_info:
+            torch.cuda.synchronize()
+            print("prediction for", coordinates.shape[0], "molecules")
+        return (energies, -grad) if forces else energies
+
+    def predict(self, X, Z, max_natoms, cells=None, inv_cells=None, forces=True, print_info=False, profiler=False):
+        n = len(X)
+        energies = torch.zeros(n, device=self.device, dtype=torch.float32)
+        all_forces = torch.zeros(n, max_natoms, 3, device=self.device, dtype=torch.float32)
+        for i in range(0, n, self.nbatch_test):
+            sl = slice(i, i + self.nbatch_test)
+            data = self.format_data(X[sl], Z[sl], cells=None if cells is None else cells[sl],
+                                    inv_cells=None if inv_cells is None else inv_cells[sl])
+            out = self.predict_opt(data['coordinates'], data['charges'], data['atomIDs'], data['molIDs'], data['natom_counts'],
+                                   data['cells'], data['inv_cells'], forces=forces)
+            if forces:
+                energies[sl] = out[0]
+                all_forces[sl, :out[1].shape[1]] = out[1]
+            else:
+                energies[sl] = out
+        return (energies, all_forces) if forces else energies
+
+    def save_jit_model(self, file_name='model_rff.pt'):
+        script = torch.jit.script(self)
+        script.save(file_name)
