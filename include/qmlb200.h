@@ -103,10 +103,12 @@ int qmlb_fchl19_backward(const float *X, const float *Z, const int *atom_counts,
 /* fchl19_representation_and_derivative_cuda / FCHLRepresentationAndDerivativeCuda
  * (cuda/fchl_cuda_kernel.cu:676-1005, 1928-1964), get_fchl_and_derivative (fchl_cuda.cpp:157-202,
  * FCHL19.cpp:152-208).  rep f32[nb,A,repsize]; jac f32[nb,A,A,3,repsize] with
- * jac[m,i,a,x,c] = d rep[m,i,c] / d r_{a,x}.  Both are fully overwritten. */
+ * jac[m,i,a,x,c] = d rep[m,i,c] / d r_{a,x}.  Both are fully overwritten.  With row_of_slot != NULL the row of
+ * centre atom (m,i) is row_of_slot[m*A+i] in both outputs (rep f32[rows,repsize], jac f32[rows,A,3,repsize]) and
+ * rows < 0 are skipped. */
 int qmlb_fchl19_forward_jacobian(const float *X, const float *Z, const int *atom_counts, int nb, int A,
-                                 const qmlb_fchl_params *p, const float *cell, const float *inv_cell, float *rep,
-                                 float *jac, qmlb_stream_t stream);
+                                 const qmlb_fchl_params *p, const float *cell, const float *inv_cell,
+                                 const int *row_of_slot, float *rep, float *jac, qmlb_stream_t stream);
 
 /* ---- element grouping (replaces the boolean-mask gathers and torch.where host syncs of
  *      models/hadamard_features.py:99-107 and models/kernel.py:141-150) -------------------- */
@@ -230,6 +232,32 @@ int qmlb_rff_predict(const float *X, const float *Z, const int *atom_counts, int
                      const float *reductors, int npcas, const float *W, const float *b, const float *alpha, int nfeatures,
                      int fast_math, size_t n_atoms_upper, void *workspace, size_t workspace_bytes, float *energy,
                      float *grad_X, qmlb_stream_t stream);
+
+/* Projection of an element-grouped explicit Jacobian: project_derivative = einsum('jmnk,kl->jmnl')
+ * (representations/dimensionality_reduction.py:61-72; call site models/kernel.py:160).
+ * jac_rows f32[rows_cap, sub_rows, repsize] (sub_rows = 3*A), out f32[rows_cap, sub_rows, npcas]. */
+int qmlb_pca_project_jacobian(const float *jac_rows, const float *reductors, const int *group_start, int nelements,
+                              size_t rows_cap, int sub_rows, int repsize, int npcas, float *out, qmlb_stream_t stream);
+
+/* ---- training rows and normal equations ------------------------------------------------------ */
+
+/* SORF training features of one batch: sorf_matrix_kernel, compute_featurisation_kernel, compute_sin_coeffs_kernel,
+ * compute_featurisation_derivative_kernel (cuda/hadamard_kernel.cu:424-717) as driven by calculate_features
+ * (models/hadamard_features.py:66-80) and build_Z_components (models/kernel.py:134-170), for all elements at once.
+ * x f32[rows_cap,N] and dx f32[rows_cap,A,3,N] are element-grouped; Dmat f32[nel,T,S,N], bias f32[nel,S*N] unpacked.
+ * Zout f64[nb,F] (overwritten) = per-molecule features; G f64[nb,A,3,F] (overwritten) = -dZ/dr, the force features
+ * (dx and G may both be NULL for energy-only training).  sinc_scratch: rows_cap*F floats.  N in [32, 1024]. */
+int qmlb_sorf_train_features(const float *x, const float *dx, const float *Dmat, const float *bias, const int *group_start,
+                             const int *slot_of_row, const int *row_of_slot, const int *atom_counts, int nelements, int nb,
+                             int A, size_t rows_cap, int N, int S, int T, float sigma, double *Zout, double *G,
+                             float *sinc_scratch, qmlb_stream_t stream);
+
+/* ZTZ += M^T M (row-major UPPER triangle only) and ZTy += M^T y for a row block M f64[rows,F]:
+ * torch.matmul(Ztrain.T, Ztrain) / torch.matmul(Ztrain.T, targets) in build_Z_components (models/kernel.py:172-192).
+ * cuBLAS DSYRK + DGEMV on `stream`.  qmlb_symmetrize_upper mirrors the triangle before the solve. */
+int qmlb_normal_equations_accumulate(const double *M, int rows, int F, const double *y, double *ZTZ, double *ZTy,
+                                     qmlb_stream_t stream);
+int qmlb_symmetrize_upper(double *ZTZ, int F, qmlb_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -31,7 +31,7 @@ SIGNATURES = {
     'qmlb_neighbour_list': (c_int, [c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p]),
     'qmlb_fchl19_forward': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, P, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     'qmlb_fchl19_backward': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, P, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
-    'qmlb_fchl19_forward_jacobian': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, P, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    'qmlb_fchl19_forward_jacobian': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, P, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     'qmlb_rows_capacity': (c_size_t, [c_size_t, c_int]),
     'qmlb_group_scratch_bytes': (c_size_t, [c_int, c_int]),
     'qmlb_group_by_element': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
@@ -53,6 +53,12 @@ SIGNATURES = {
     'qmlb_rff_predict': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, P, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                  c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_size_t, c_void_p, c_size_t, c_void_p,
                                  c_void_p, c_void_p]),
+    'qmlb_pca_project_jacobian': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_int, c_int, c_int, c_void_p, c_void_p]),
+    'qmlb_sorf_train_features': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                         c_int, c_int, c_size_t, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p,
+                                         c_void_p]),
+    'qmlb_normal_equations_accumulate': (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    'qmlb_symmetrize_upper': (c_int, [c_void_p, c_int, c_void_p]),
 }
 
 _lib = None

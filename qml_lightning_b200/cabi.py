@@ -132,15 +132,22 @@ def fchl19_backward(X, Z, atom_counts, params, grad_rep, cell=None, inv_cell=Non
     return (grad_X, mol_energy) if atom_energy is not None else grad_X
 
 
-def fchl19_forward_jacobian(X, Z, atom_counts, params, cell=None, inv_cell=None):
+def fchl19_forward_jacobian(X, Z, atom_counts, params, cell=None, inv_cell=None, grouping=None):
+    """Representation and explicit Jacobian; in element-grouped row order when ``grouping`` is given."""
     X, Z, atom_counts, nb, A = _batch(X, Z, atom_counts)
     cell, inv_cell = _cells(cell, inv_cell)
-    rep = torch.empty(nb, A, params.repsize, dtype=torch.float32, device=X.device)
-    jac = torch.empty(nb, A, A, 3, params.repsize, dtype=torch.float32, device=X.device)
+    if grouping is None:
+        rep = torch.empty(nb, A, params.repsize, dtype=torch.float32, device=X.device)
+        jac = torch.empty(nb, A, A, 3, params.repsize, dtype=torch.float32, device=X.device)
+        ros = None
+    else:
+        rep = torch.zeros(grouping.rows_cap, params.repsize, dtype=torch.float32, device=X.device)
+        jac = torch.zeros(grouping.rows_cap, A, 3, params.repsize, dtype=torch.float32, device=X.device)
+        ros = grouping.row_of_slot
     pc = params.c()
     check(_lib.load().qmlb_fchl19_forward_jacobian(_p(X, torch.float32, 'coordinates'), _p(Z, torch.float32, 'charges'),
                                                    _p(atom_counts, torch.int32, 'atom_counts'), nb, A, ctypes.byref(pc),
-                                                   _p(cell), _p(inv_cell), _p(rep), _p(jac), _stream(X.device)),
+                                                   _p(cell), _p(inv_cell), _p(ros), _p(rep), _p(jac), _stream(X.device)),
           'qmlb_fchl19_forward_jacobian')
     return rep, jac
 
@@ -342,3 +349,44 @@ def rff_predict(X, Z, atom_counts, fchl, elements, reductors, W, b, alpha, cell=
                                _p(alpha.contiguous(), torch.float32, 'alpha'), D, int(bool(fast_math)), upper, _p(ws),
                                ws.numel(), _p(energy), _p(grad_X), _stream(X.device)), 'qmlb_rff_predict')
     return energy, grad_X
+
+
+def pca_project_jacobian(jac_rows, reductors, grouping):
+    """``[rows, A, 3, repsize] -> [rows, A, 3, npcas]`` on element-grouped rows."""
+    nel, repsize, npcas = reductors.shape
+    rows, A = jac_rows.shape[0], jac_rows.shape[1]
+    out = torch.empty(rows, A, 3, npcas, dtype=torch.float32, device=jac_rows.device)
+    check(_lib.load().qmlb_pca_project_jacobian(_p(jac_rows, torch.float32, 'jac_rows'), _p(reductors.contiguous(), torch.float32, 'reductors'),
+                                                _p(grouping.group_start), nel, rows, 3 * A, repsize, npcas, _p(out),
+                                                _stream(jac_rows.device)), 'qmlb_pca_project_jacobian')
+    return out
+
+
+def sorf_train_features(x, dx, Dmat, bias, grouping, atom_counts, nb, A, sigma):
+    """Per-molecule features ``Z f64[nb,F]`` and force features ``G f64[nb,A,3,F]`` (``None`` without ``dx``)."""
+    nel, T, S, N = Dmat.shape
+    F = S * N
+    dev = x.device
+    Z = torch.empty(nb, F, dtype=torch.float64, device=dev)
+    G = torch.empty(nb, A, 3, F, dtype=torch.float64, device=dev) if dx is not None else None
+    sinc = torch.empty(grouping.rows_cap, F, dtype=torch.float32, device=dev)
+    check(_lib.load().qmlb_sorf_train_features(_p(x, torch.float32, 'x'), _p(dx, torch.float32, 'dx'),
+                                               _p(Dmat.contiguous(), torch.float32, 'Dmat'), _p(bias.contiguous(), torch.float32, 'bias'),
+                                               _p(grouping.group_start), _p(grouping.slot_of_row), _p(grouping.row_of_slot),
+                                               _p(atom_counts.contiguous(), torch.int32, 'atom_counts'), nel, nb, A,
+                                               grouping.rows_cap, N, S, T, float(sigma), _p(Z), _p(G), _p(sinc), _stream(dev)),
+          'qmlb_sorf_train_features')
+    return Z, G
+
+
+def normal_equations_accumulate(M, y, ZTZ, ZTy):
+    """``ZTZ += M^T M`` (upper triangle) and ``ZTy += M^T y`` in float64."""
+    rows, F = M.shape
+    check(_lib.load().qmlb_normal_equations_accumulate(_p(M.contiguous(), torch.float64, 'M'), rows, F,
+                                                       _p(None if y is None else y.contiguous(), torch.float64, 'y'),
+                                                       _p(ZTZ, torch.float64, 'ZTZ'), _p(ZTy, torch.float64, 'ZTy'),
+                                                       _stream(M.device)), 'qmlb_normal_equations_accumulate')
+
+
+def symmetrize_upper(ZTZ):
+    check(_lib.load().qmlb_symmetrize_upper(_p(ZTZ, torch.float64, 'ZTZ'), ZTZ.shape[0], _stream(ZTZ.device)), 'qmlb_symmetrize_upper')

@@ -470,7 +470,7 @@ __global__ void __launch_bounds__(FCHL_THREADS)
 fchl_jacobian_kernel(const float *__restrict__ X, const float *__restrict__ Z, const int *__restrict__ counts,
                      const float *__restrict__ species, const float *__restrict__ Rs2, const float *__restrict__ Rs3,
                      const float *__restrict__ cell, const float *__restrict__ icell, FchlK K,
-                     float *__restrict__ rep, float *__restrict__ jac) {
+                     const int *__restrict__ row_of_slot, float *__restrict__ rep, float *__restrict__ jac) {
     extern __shared__ __align__(16) float sm[];
     const int mol = blockIdx.x, A = K.A;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -485,8 +485,10 @@ fchl_jacobian_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
     const size_t R = K.repsize;
 
     for (int i = warp; i < A; i += FCHL_WARPS) {
-        float *dst = rep + ((size_t)mol * A + i) * R;
-        float *J = jac + ((size_t)mol * A + i) * (size_t)A * 3 * R;  // [a][x][c]
+        const long row = row_of_slot ? (long)row_of_slot[(size_t)mol * A + i] : (long)mol * A + i;
+        if (row < 0) continue;
+        float *dst = rep + (size_t)row * R;
+        float *J = jac + (size_t)row * (size_t)A * 3 * R;  // [a][x][c]
         for (size_t c = lane; c < (size_t)A * 3 * R; c += 32) J[c] = 0.f;
         if (i >= natoms) {
             for (int c = lane; c < K.repsize; c += 32) dst[c] = 0.f;
@@ -694,7 +696,7 @@ extern "C" int qmlb_fchl19_backward(const float *X, const float *Z, const int *a
 
 extern "C" int qmlb_fchl19_forward_jacobian(const float *X, const float *Z, const int *atom_counts, int nb, int A,
                                             const qmlb_fchl_params *p, const float *cell, const float *inv_cell,
-                                            float *rep, float *jac, qmlb_stream_t stream) {
+                                            const int *row_of_slot, float *rep, float *jac, qmlb_stream_t stream) {
     FchlK K;
     if (int rc = make_K(p, nb, A, cell, inv_cell, K)) return rc;
     QMLB_REQUIRE(X && Z && atom_counts && rep && jac, "qmlb_fchl19_forward_jacobian: null tensor");
@@ -702,7 +704,7 @@ extern "C" int qmlb_fchl19_forward_jacobian(const float *X, const float *Z, cons
     const Layout L(A, K.nRs2, K.nRs3, K.repsize, false);
     if (int rc = qmlb::ensure_smem(fchl_jacobian_kernel, L.bytes(), "qmlb_fchl19_forward_jacobian")) return rc;
     fchl_jacobian_kernel<<<nb, FCHL_THREADS, L.bytes(), qmlb::as_stream(stream)>>>(
-        X, Z, atom_counts, p->species, p->Rs2, p->Rs3, cell, inv_cell, K, rep, jac);
+        X, Z, atom_counts, p->species, p->Rs2, p->Rs3, cell, inv_cell, K, row_of_slot, rep, jac);
     return qmlb::check_launch("qmlb_fchl19_forward_jacobian");
 }
 

@@ -16,13 +16,16 @@ constexpr int BM = QMLB_ROW_TILE, BN = 64, BK = 16, PAD = 4;
 template <bool TRANS>
 __global__ void __launch_bounds__(256)
 pca_gemm_kernel(const float *__restrict__ in, const float *__restrict__ P, const int *__restrict__ group_start, int nel,
-                int K, int Nout, int npcas, size_t p_stride, float *__restrict__ out) {
+                int K, int Nout, int npcas, size_t p_stride, int sub_rows, float *__restrict__ out) {
     __shared__ __align__(16) float As[BK][BM + PAD];
     __shared__ __align__(16) float Bs[BK][BN + PAD];
-    const int row0 = blockIdx.x * BM, col0 = blockIdx.y * BN;
-    if (row0 >= group_start[nel]) return;
+    // `sub_rows` matrix rows belong to every grouped row (1 for representations, 3*natoms for Jacobians), so the group
+    // boundaries scale with it and stay tile aligned.
+    const long row0 = (long)blockIdx.x * BM;
+    const int col0 = blockIdx.y * BN;
+    if (row0 >= (long)group_start[nel] * sub_rows) return;
     int e = 0;
-    while (e + 1 < nel && row0 >= group_start[e + 1]) ++e;
+    while (e + 1 < nel && row0 >= (long)group_start[e + 1] * sub_rows) ++e;
     const float *Pe = P + (size_t)e * p_stride;
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     float acc[4][4] = {};
@@ -94,9 +97,24 @@ extern "C" int qmlb_pca_project(const float *in, const float *reductors, const i
     const size_t p_stride = (size_t)repsize * npcas;
     if (transpose)
         pca_gemm_kernel<true><<<grid, 256, 0, qmlb::as_stream(stream)>>>(in, reductors, group_start, nelements, K, Nout,
-                                                                         npcas, p_stride, out);
+                                                                         npcas, p_stride, 1, out);
     else
         pca_gemm_kernel<false><<<grid, 256, 0, qmlb::as_stream(stream)>>>(in, reductors, group_start, nelements, K, Nout,
-                                                                          npcas, p_stride, out);
+                                                                          npcas, p_stride, 1, out);
     return qmlb::check_launch("qmlb_pca_project");
+}
+
+extern "C" int qmlb_pca_project_jacobian(const float *jac_rows, const float *reductors, const int *group_start,
+                                         int nelements, size_t rows_cap, int sub_rows, int repsize, int npcas, float *out,
+                                         qmlb_stream_t stream) {
+    QMLB_REQUIRE(jac_rows && reductors && group_start && out, "qmlb_pca_project_jacobian: null tensor");
+    QMLB_REQUIRE(nelements > 0 && repsize > 0 && npcas > 0 && sub_rows > 0, "qmlb_pca_project_jacobian: bad sizes");
+    QMLB_REQUIRE(rows_cap % BM == 0, "qmlb_pca_project_jacobian: rows_cap must be a multiple of %d", BM);
+    if (rows_cap == 0) return QMLB_OK;
+    const size_t mrows = rows_cap * (size_t)sub_rows;
+    QMLB_REQUIRE(mrows / BM < ((size_t)1 << 31), "qmlb_pca_project_jacobian: too many rows");
+    dim3 grid((unsigned)(mrows / BM), (unsigned)((npcas + BN - 1) / BN));
+    pca_gemm_kernel<false><<<grid, 256, 0, qmlb::as_stream(stream)>>>(jac_rows, reductors, group_start, nelements, repsize,
+                                                                      npcas, npcas, (size_t)repsize * npcas, sub_rows, out);
+    return qmlb::check_launch("qmlb_pca_project_jacobian");
 }

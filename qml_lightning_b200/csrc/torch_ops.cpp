@@ -197,7 +197,7 @@ std::vector<Tensor> get_fchl_and_derivative(Tensor X, Tensor Z, Tensor species, 
     }
     Tensor jac = torch::empty({b.nb, b.A, b.A, 3, f.repsize()}, b.X.options());
     check(qmlb_fchl19_forward_jacobian(b.X.data_ptr<float>(), b.Z.data_ptr<float>(), b.counts.data_ptr<int>(), b.nb, b.A,
-                                       &f.p, cell_ptr(b.cell), cell_ptr(b.inv_cell), rep.data_ptr<float>(),
+                                       &f.p, cell_ptr(b.cell), cell_ptr(b.inv_cell), nullptr, rep.data_ptr<float>(),
                                        jac.data_ptr<float>(), current_stream()),
           "get_fchl_and_derivative");
     return {rep, jac};

@@ -164,3 +164,81 @@ class BaseKernel():
 
     def _parameters_changed(self):
         """Hook for subclasses that cache derived parameter buffers."""
+
+    # ---- training --------------------------------------------------------------------------------------------
+    def training_rows(self, data, with_forces):
+        """``(Z f64[zbatch,F], G f64[zbatch,A,3,F] | None)`` for one formatted batch; implemented by the models."""
+        raise NotImplementedError("Abstract method only.")
+
+    @staticmethod
+    def allreduce_normal_equations(ZTZ, ZtrainY):
+        """Sum the per-rank partial normal equations in place (no-op without an initialised process group)."""
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(ZTZ, op=dist.ReduceOp.SUM)
+            dist.all_reduce(ZtrainY, op=dist.ReduceOp.SUM)
+        return ZTZ, ZtrainY
+
+    def build_Z_components(self, X, Q, E=None, F=None, cells=None, inv_cells=None, print_info=True, cpu_solve=False, ntiles=1,
+                           use_specialized_matmul=False, distributed=False):
+        """Accumulate ``Z^T Z`` (float64) and ``Z^T y`` over host batches of ``nbatch_train`` molecules.
+
+        Rows per molecule: one energy row and, with forces, ``3 * max_atoms`` force rows (``G = -dZ/dr``), targets
+        ``cat(E, F.flatten())`` -- the construction of upstream build_Z_components (kernel.py:46-217).  Only the upper
+        triangle is accumulated (DSYRK) and mirrored once at the end.  With ``distributed=True`` every rank of the
+        initialised process group takes a contiguous, atom-balanced share of the molecules and the partial sums are
+        combined with one all-reduce.  ``ntiles`` and ``use_specialized_matmul`` are accepted for signature
+        compatibility: the full matrix is kept on the device.
+        """
+        from .. import cabi
+        from ..utils.sharding import my_shard
+        if E is None and F is None:
+            raise RuntimeError("must have either E, F or both as input to train().")
+        lo, hi = 0, len(X)
+        if distributed:
+            import torch.distributed as dist
+            lo, hi = my_shard([np.asarray(q).shape[0] for q in Q], dist.get_rank(), dist.get_world_size())
+        dev = self.rep.device
+        nf = self.nfeatures()
+        ZTZ = torch.zeros(nf, nf, device=dev, dtype=torch.float64)
+        ZtrainY = torch.zeros(nf, 1, device=dev, dtype=torch.float64)
+        for i in range(lo, hi, self.nbatch_train):
+            sl = slice(i, min(i + self.nbatch_train, hi))
+            data = self.format_data(X[sl], Q[sl], E=None if E is None else E[sl], F=None if F is None else F[sl],
+                                    cells=None if cells is None else cells[sl],
+                                    inv_cells=None if inv_cells is None else inv_cells[sl])
+            zbatch = data['coordinates'].shape[0]
+            Ztrain, Gtrain = self.training_rows(data, with_forces=F is not None)
+            if E is None:
+                Ztrain.zero_()       # energy rows must not contribute when only forces are fitted (kernel.py:164-165)
+                targets = torch.cat((torch.zeros(zbatch, dtype=torch.float64, device=dev), data['forces'].flatten()))
+            elif F is None:
+                targets = data['energies']
+            else:
+                targets = torch.cat((data['energies'], data['forces'].flatten()))
+            rows = Ztrain if Gtrain is None else torch.cat((Ztrain, Gtrain.reshape(-1, nf)), dim=0)
+            cabi.normal_equations_accumulate(rows, targets.contiguous(), ZTZ, ZtrainY)
+        cabi.symmetrize_upper(ZTZ)
+        if distributed:
+            self.allreduce_normal_equations(ZTZ, ZtrainY)
+        if cpu_solve:
+            ZTZ = ZTZ.cpu()
+        return ZTZ, ZtrainY
+
+    def train(self, X, Q, E=None, F=None, cells=None, inv_cells=None, print_info=True, cpu_solve=False, ntiles=1,
+              use_specialized_matmul=False, distributed=False):
+        """Solve ``(Z^T Z + llambda I) alpha = Z^T y`` (upstream kernel.py:219-247).  The system is symmetric positive
+        definite, so a Cholesky factorisation replaces upstream's LU; LU is the fallback if the factorisation fails."""
+        ZTZ, ZtrainY = self.build_Z_components(X, Q, E, F, cells, inv_cells, print_info, cpu_solve, ntiles,
+                                               use_specialized_matmul, distributed)
+        ZTZ.diagonal().add_(self.llambda)
+        rhs = ZtrainY.to(ZTZ.device)
+        L, info = torch.linalg.cholesky_ex(ZTZ)
+        if int(info) == 0:
+            alpha = torch.cholesky_solve(rhs, L)[:, 0]
+        else:
+            alpha = torch.linalg.solve(ZTZ, rhs)[:, 0]
+        self.alpha = alpha.to(self.rep.device)
+        self.is_trained = True
+        self._parameters_changed()
+        del ZTZ, ZtrainY
