@@ -130,33 +130,37 @@ __device__ int build_neighbours(const float *sm, float *ws, const FchlK &K, int 
         const unsigned m = __ballot_sync(QMLB_FULL_MASK, ok);
         if (ok) {
             const int pos = nn + __popc(m & ((1u << lane) - 1u));
+            // Distance and the two logarithms of the log-normal parameters in double (their rounding is amplified
+            // by 1/sigma^2 in the exponent); everything else is well conditioned and stays in float.
             const double rd = sqrt((double)dx * dx + (double)dy * dy + (double)dz * dz);
             const float r = (float)rd;
-            const double pi = 3.14159265358979323846;
-            const double arg = rd * pi / (double)K.rcut;
-            const double fc = 0.5 * (cos(arg) + 1.0);
-            const double dfc = -0.5 * sin(arg) * pi / (double)K.rcut;
+            const float inv_rcut = 1.0f / K.rcut;
+            float sarg, carg;
+            sincospif(r * inv_rcut, &sarg, &carg);
+            const float fc = 0.5f * (carg + 1.0f);
+            const float dfc = -0.5f * sarg * 3.14159265358979f * inv_rcut;
             const double eta = (double)K.eta2;
-            const double t = 1.0 + eta / (rd * rd);
-            const double s2 = log(t);
-            const double mu = log(rd / sqrt(t));
-            const double ds2 = -2.0 * eta / (rd * (rd * rd + eta));
-            const double dmu = (rd * rd + 2.0 * eta) / (rd * (rd * rd + eta));
+            const double s2 = log1p(eta / (rd * rd));
+            const double mu = log(rd) - 0.5 * s2;
+            const float rf2 = r * r;
+            const float s2f = (float)s2;
+            const float ds2 = -2.0f * K.eta2 / (r * (rf2 + K.eta2));
+            const float dmu = (rf2 + 2.0f * K.eta2) / (r * (rf2 + K.eta2));
             n_idx[pos] = j;
             n_et[pos] = set[j];
             ws[F_DX * A + pos] = dx;
             ws[F_DY * A + pos] = dy;
             ws[F_DZ * A + pos] = dz;
             ws[F_R * A + pos] = r;
-            ws[F_FC * A + pos] = (float)fc;
-            ws[F_DFC * A + pos] = (float)dfc;
+            ws[F_FC * A + pos] = fc;
+            ws[F_DFC * A + pos] = dfc;
             ws[F_MU * A + pos] = (float)mu;
             ws[F_MULO * A + pos] = (float)(mu - (double)(float)mu);
-            ws[F_I2S * A + pos] = (float)(0.5 / s2);
-            ws[F_PREF * A + pos] = (float)(pow(rd, -(double)K.d2) / (sqrt(s2) * 2.5066282746310002));
-            ws[F_C0 * A + pos] = (float)(-0.5 * ds2 / s2 - (double)K.d2 / rd);
-            ws[F_C1 * A + pos] = (float)(dmu / s2);
-            ws[F_C2 * A + pos] = (float)(ds2 / (2.0 * s2 * s2));
+            ws[F_I2S * A + pos] = 0.5f / s2f;
+            ws[F_PREF * A + pos] = powf(r, -K.d2) * rsqrtf(s2f) * 0.3989422804014327f;  // 1 / (sigma sqrt(2 pi))
+            ws[F_C0 * A + pos] = -0.5f * ds2 / s2f - K.d2 / r;
+            ws[F_C1 * A + pos] = dmu / s2f;
+            ws[F_C2 * A + pos] = ds2 / (2.0f * s2f * s2f);
         }
         nn += __popc(m);
     }
@@ -219,7 +223,7 @@ __device__ __forceinline__ void triplet_geometry(const float *ws, int A, int j, 
     g.sth = fminf(1.0f, sab / ab);
     g.w = ab / fmaxf(sab, 1e-5f);
     g.T = 1.0f + 3.0f * g.ci * g.cj * g.ck;
-    g.R = powf(g.a * g.b * g.c, -K.d3);
+    g.R = exp2f(-K.d3 * __log2f(g.a * g.b * g.c));  // (r_ij r_ik r_jk)^-d3; the SFU log2 is exact to ~2e-7 relative here
     g.Fij = ws[F_FC * A + j];
     g.Fik = ws[F_FC * A + k];
     g.dFij = ws[F_DFC * A + j];
@@ -373,12 +377,17 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
         }
         __syncwarp();
 
-        // three-body: one triplet per lane, radial grid serial
+        // three-body: one triplet per lane, radial grid serial.  Triplets are enumerated row-major in (j,k), so the
+        // lanes that share j form one contiguous run per warp: their contributions to atom j are combined with a
+        // segmented shuffle reduction and added once by the run's first lane (runs have distinct j, so no atomics);
+        // contributions to atom k collide at most between runs and use shared-memory atomics.
         const int ntrip = nn * (nn - 1) / 2;
         for (int t0 = 0; t0 < ntrip; t0 += 32) {
             const int t = t0 + lane;
-            if (t < ntrip) {
-                int j, k;
+            const bool active = t < ntrip;
+            int j = 0, k = 1;
+            float fj0 = 0.f, fj1 = 0.f, fj2 = 0.f;
+            if (active) {
                 decode_pair(t, nn, j, k);
                 TripletGeom g;
                 triplet_geometry(ws, A, j, k, K, g);
@@ -421,15 +430,38 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
                 fi0 += ga * eij0 + gbb * eik0;
                 fi1 += ga * eij1 + gbb * eik1;
                 fi2 += ga * eij2 + gbb * eik2;
-                float *fj = force + 3 * n_idx[j];
+                fj0 = -ga * eij0 + gcc * g.ejk[0];
+                fj1 = -ga * eij1 + gcc * g.ejk[1];
+                fj2 = -ga * eij2 + gcc * g.ejk[2];
                 float *fk = force + 3 * n_idx[k];
-                atomicAdd(fj + 0, -ga * eij0 + gcc * g.ejk[0]);
-                atomicAdd(fj + 1, -ga * eij1 + gcc * g.ejk[1]);
-                atomicAdd(fj + 2, -ga * eij2 + gcc * g.ejk[2]);
                 atomicAdd(fk + 0, -gbb * eik0 - gcc * g.ejk[0]);
                 atomicAdd(fk + 1, -gbb * eik1 - gcc * g.ejk[1]);
                 atomicAdd(fk + 2, -gbb * eik2 - gcc * g.ejk[2]);
             }
+            __syncwarp();
+            // segmented reduction over the run of lanes with equal j
+            const bool head = active && (lane == 0 || k == j + 1);
+            const unsigned heads = __ballot_sync(QMLB_FULL_MASK, head || !active);
+            const unsigned above = lane == 31 ? 0u : (heads & ~((2u << lane) - 1u));
+            const int last = above ? __ffs(above) - 2 : 31;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const float o0 = __shfl_down_sync(QMLB_FULL_MASK, fj0, off);
+                const float o1 = __shfl_down_sync(QMLB_FULL_MASK, fj1, off);
+                const float o2 = __shfl_down_sync(QMLB_FULL_MASK, fj2, off);
+                if (lane + off <= last) {
+                    fj0 += o0;
+                    fj1 += o1;
+                    fj2 += o2;
+                }
+            }
+            if (head) {
+                float *fj = force + 3 * n_idx[j];
+                atomicAdd(fj + 0, fj0);   // uncontended: one head per j in this pass
+                atomicAdd(fj + 1, fj1);
+                atomicAdd(fj + 2, fj2);
+            }
+            __syncwarp();
         }
         fi0 = warp_sum(fi0);
         fi1 = warp_sum(fi1);
