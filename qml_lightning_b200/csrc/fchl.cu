@@ -29,19 +29,20 @@ struct FchlK {
 // block : x[A] y[A] z[A] et[A] | Rs2[nRs2] logRs2[nRs2] invRs2[nRs2] Rs3[nRs3] | cell[9] icell[9] | logRs2_lo[nRs2] (+pad)
 // ln Rs2 and mu are kept as float pairs (hi + lo): the log-normal exponent (ln Rs2 - mu)^2 / (2 sigma^2) amplifies
 // the rounding of its argument by up to 1/sigma^2 ~ 100, which would otherwise cost a digit of the representation.
-// warp  : NB_FIELDS arrays of A entries | row[repsize] | (backward) force[3A]
+// warp  : NB_FIELDS arrays of A entries | row[repsize] | (backward) force[3A] | 32 x float4 triplet staging
 constexpr int NB_FIELDS = 15;
 enum { F_IDX = 0, F_DX, F_DY, F_DZ, F_R, F_FC, F_DFC, F_ET, F_MU, F_MULO, F_I2S, F_PREF, F_C0, F_C1, F_C2 };
 
 __host__ __device__ inline int align4(int v) { return (v + 3) & ~3; }
 
 struct Layout {
-    int block_floats, warp_floats, off_row, off_force;
+    int block_floats, warp_floats, off_row, off_force, off_stage;
     __host__ __device__ Layout(int A, int nRs2, int nRs3, int repsize, bool backward) {
         block_floats = align4(4 * A + 4 * nRs2 + nRs3 + 18);
         off_row = align4(NB_FIELDS * A);
         off_force = off_row + align4(repsize);
-        warp_floats = off_force + (backward ? align4(3 * A) : 0);
+        off_stage = off_force + (backward ? align4(3 * A) : 0);
+        warp_floats = off_stage + 128;   // 32 staged triplets x float4
     }
     __host__ __device__ size_t bytes() const { return sizeof(float) * ((size_t)block_floats + (size_t)FCHL_WARPS * warp_floats); }
 };
@@ -179,11 +180,6 @@ __device__ __forceinline__ void decode_pair(int t, int n, int &j, int &k) {
     k = t - (jj * (2 * n - jj - 1)) / 2 + jj + 1;
 }
 
-struct Triplet {
-    float rbar, a_cos, a_sin;  // forward amplitudes
-    int sidx;                  // first column of the (element pair) block
-};
-
 // Scalars of one triplet (i; j,k) that the backward pass needs on top of the forward amplitudes.
 struct TripletGeom {
     float a, b, c;          // r_ij, r_ik, r_jk
@@ -276,36 +272,57 @@ fchl_forward_kernel(const float *__restrict__ X, const float *__restrict__ Z, co
             }
         }
 
-        // three-body (fchl_cuda_kernel.cu:605-672): 32 triplets at a time, one per lane for the scalar part,
-        // then each triplet is broadcast and the lanes cover the radial grid.
+        // three-body (fchl_cuda_kernel.cu:605-672): 32 triplets at a time, one per lane for the scalar part; their
+        // (rbar, amplitudes, block offset) go to a small per-warp staging area, then each triplet is read back as
+        // one broadcast 128-bit load and the lanes cover the radial grid (exp2 with the constant folded in).
         const int ntrip = nn * (nn - 1) / 2;
+        float4 *stage = reinterpret_cast<float4 *>(ws + L.off_stage);
+        const float c_exp = -K.eta3 * 1.4426950408889634f;
+        const bool pair_ok = ((K.nel * K.nRs2) & 1) == 0;   // (cos, sin) columns 8-byte aligned
         for (int t0 = 0; t0 < ntrip; t0 += 32) {
             const int t = t0 + lane;
-            Triplet tr = {0.f, 0.f, 0.f, 0};
+            float4 tr = make_float4(0.f, 0.f, 0.f, 0.f);
             if (t < ntrip) {
                 int j, k;
                 decode_pair(t, nn, j, k);
                 TripletGeom g;
                 triplet_geometry(ws, A, j, k, K, g);
                 const float amp = ZETA2 * K.w3 * g.T * g.R * g.Fij * g.Fik;
-                tr.rbar = 0.5f * (g.a + g.b);
-                tr.a_cos = amp * g.cth;
-                tr.a_sin = amp * g.sth;
-                tr.sidx = pair_block(n_et[j], n_et[k], K);
+                tr.x = 0.5f * (g.a + g.b);
+                tr.y = amp * g.cth;
+                tr.z = amp * g.sth;
+                tr.w = __int_as_float(pair_block(n_et[j], n_et[k], K));
             }
+            stage[lane] = tr;
+            __syncwarp();
             const int cnt = min(32, ntrip - t0);
-            for (int q = 0; q < cnt; ++q) {
-                const float rbar = __shfl_sync(QMLB_FULL_MASK, tr.rbar, q);
-                const float ac = __shfl_sync(QMLB_FULL_MASK, tr.a_cos, q);
-                const float as = __shfl_sync(QMLB_FULL_MASK, tr.a_sin, q);
-                const int sidx = __shfl_sync(QMLB_FULL_MASK, tr.sidx, q);
-                for (int l = lane; l < K.nRs3; l += 32) {
-                    const float d = rbar - sRs3[l];
-                    const float radial = expf(-K.eta3 * d * d);
-                    acc[sidx + 2 * l] += radial * ac;
-                    acc[sidx + 2 * l + 1] += radial * as;
+            if (K.nRs3 <= 32 && pair_ok) {
+                const float rs = lane < K.nRs3 ? sRs3[lane] : 0.f;
+                for (int q = 0; q < cnt; ++q) {
+                    const float4 b = stage[q];
+                    if (lane < K.nRs3) {
+                        const float d = b.x - rs;
+                        const float radial = exp2f(c_exp * d * d);
+                        float2 *p2 = reinterpret_cast<float2 *>(acc + __float_as_int(b.w)) + lane;
+                        float2 v = *p2;
+                        v.x = fmaf(radial, b.y, v.x);
+                        v.y = fmaf(radial, b.z, v.y);
+                        *p2 = v;
+                    }
+                }
+            } else {
+                for (int q = 0; q < cnt; ++q) {
+                    const float4 b = stage[q];
+                    const int sidx = __float_as_int(b.w);
+                    for (int l = lane; l < K.nRs3; l += 32) {
+                        const float d = b.x - sRs3[l];
+                        const float radial = exp2f(c_exp * d * d);
+                        acc[sidx + 2 * l] += radial * b.y;
+                        acc[sidx + 2 * l + 1] += radial * b.z;
+                    }
                 }
             }
+            __syncwarp();
         }
         __syncwarp();
         for (int c = lane; c < K.repsize; c += 32) dst[c] = acc[c];
@@ -382,6 +399,8 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
         // segmented shuffle reduction and added once by the run's first lane (runs have distinct j, so no atomics);
         // contributions to atom k collide at most between runs and use shared-memory atomics.
         const int ntrip = nn * (nn - 1) / 2;
+        const float c_exp = -K.eta3 * 1.4426950408889634f;
+        const bool pair_ok = ((K.nel * K.nRs2) & 1) == 0;   // (cos, sin) gradient columns 8-byte aligned
         for (int t0 = 0; t0 < ntrip; t0 += 32) {
             const int t = t0 + lane;
             const bool active = t < ntrip;
@@ -396,13 +415,26 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
                 const float rbar = 0.5f * (g.a + g.b);
                 const float *gb = grow + pair_block(n_et[j], n_et[k], K);
                 float Gc = 0.f, Gs = 0.f, Gr = 0.f;
-                for (int l = 0; l < K.nRs3; ++l) {
-                    const float d = rbar - sRs3[l];
-                    const float radial = expf(-K.eta3 * d * d);
-                    const float gc = gb[2 * l] * radial, gs = gb[2 * l + 1] * radial;
-                    Gc += gc;
-                    Gs += gs;
-                    Gr += (gc * a_cos + gs * a_sin) * d;
+                if (pair_ok) {
+                    const float2 *gb2 = reinterpret_cast<const float2 *>(gb);
+                    for (int l = 0; l < K.nRs3; ++l) {
+                        const float d = rbar - sRs3[l];
+                        const float radial = exp2f(c_exp * d * d);
+                        const float2 gg = gb2[l];
+                        const float gc = gg.x * radial, gs = gg.y * radial;
+                        Gc += gc;
+                        Gs += gs;
+                        Gr = fmaf(fmaf(gc, a_cos, gs * a_sin), d, Gr);
+                    }
+                } else {
+                    for (int l = 0; l < K.nRs3; ++l) {
+                        const float d = rbar - sRs3[l];
+                        const float radial = exp2f(c_exp * d * d);
+                        const float gc = gb[2 * l] * radial, gs = gb[2 * l + 1] * radial;
+                        Gc += gc;
+                        Gs += gs;
+                        Gr = fmaf(fmaf(gc, a_cos, gs * a_sin), d, Gr);
+                    }
                 }
                 Gr *= -2.0f * K.eta3;
                 // d/d(cos theta_i), d/dK
