@@ -22,7 +22,13 @@
 
 namespace {
 
-constexpr int WARPS = 8;
+#ifndef SORF_WARPS
+#define SORF_WARPS 4
+#endif
+#ifndef SORF_MINB
+#define SORF_MINB 4
+#endif
+constexpr int WARPS = SORF_WARPS;
 constexpr int ROWSTRIDE = 20;  // floats per 16-element row in the transposition slab
 
 template <int LOG2N>
@@ -158,7 +164,7 @@ __device__ __forceinline__ void load16_row(float (&v)[16], const float *p) {
 }
 
 template <int LOG2N, bool FAST, int TT>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, SORF_MINB)
 sorf_energy_grad_kernel(const float *__restrict__ x, const int *__restrict__ group_start,
                         const int *__restrict__ slot_of_row, int nel, int S, int T_rt, float scale,
                         const float *__restrict__ Dp, const float *__restrict__ bp, const float *__restrict__ ap,
@@ -195,42 +201,60 @@ sorf_energy_grad_kernel(const float *__restrict__ x, const int *__restrict__ gro
         const int sc = s0 + g;
         const float *Ds = Dp_e + (size_t)sc * T * N + pos;
         float u[16], c[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) u[e] = xr[e];
         bool in_a = true;
+        if (TT == 1) {
+            // single transform: the sign diagonal stays in registers for the way back
+            load16<C::L>(c, Ds);
 #pragma unroll
-        for (int m = 0; m < T; ++m) {
-            load16<C::L>(c, Ds + (size_t)m * N);
+            for (int e = 0; e < 16; ++e) u[e] = xr[e] * c[e];
+            fwht_flip<LOG2N>(u, slab, l, lane, true);
+            in_a = false;
+        } else {
 #pragma unroll
-            for (int e = 0; e < 16; ++e) u[e] *= c[e];
-            fwht_flip<LOG2N>(u, slab, l, lane, in_a);
-            in_a = !in_a;
-        }
-        {   // features: energy contribution and d/d(arg), in the layout the forward transform ended in
-            float a[16];
-            load16<C::L>(c, bp_e + (size_t)sc * N + pos);
-            load16<C::L>(a, ap + (size_t)sc * N + pos);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) {
-                const float arg = fmaf(u[e], scale, c[e]);
-                float sn, cs;
-                if (FAST) __sincosf(arg, &sn, &cs);
-                else sincosf(arg, &sn, &cs);
-                eacc = fmaf(a[e], cs, eacc);
-                u[e] = -a[e] * sn;
-            }
-        }
-#pragma unroll
-        for (int m = T - 1; m >= 0; --m) {
-            fwht_flip<LOG2N>(u, slab, l, lane, in_a);
-            in_a = !in_a;
-            load16<C::L>(c, Ds + (size_t)m * N);
-            if (m > 0) {
+            for (int e = 0; e < 16; ++e) u[e] = xr[e];
+            for (int m = 0; m < T; ++m) {
+                load16<C::L>(c, Ds + (size_t)m * N);
 #pragma unroll
                 for (int e = 0; e < 16; ++e) u[e] *= c[e];
-            } else {
+                fwht_flip<LOG2N>(u, slab, l, lane, in_a);
+                in_a = !in_a;
+            }
+        }
+        {   // features: energy contribution and d/d(arg), in the layout the forward transform ended in
+            const float4 *bq = reinterpret_cast<const float4 *>(bp_e + (size_t)sc * N + pos);
+            const float4 *aq = reinterpret_cast<const float4 *>(ap + (size_t)sc * N + pos);
 #pragma unroll
-                for (int e = 0; e < 16; ++e) gx[e] = fmaf(u[e], c[e], gx[e]);
+            for (int q = 0; q < 4; ++q) {
+                const float4 b4 = __ldg(bq + q * C::L), a4 = __ldg(aq + q * C::L);
+                const float bb[4] = {b4.x, b4.y, b4.z, b4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const int e = 4 * q + r;
+                    const float arg = fmaf(u[e], scale, bb[r]);
+                    float sn, cs;
+                    if (FAST) __sincosf(arg, &sn, &cs);
+                    else sincosf(arg, &sn, &cs);
+                    eacc = fmaf(aa[r], cs, eacc);
+                    u[e] = -aa[r] * sn;
+                }
+            }
+        }
+        if (TT == 1) {
+            fwht_flip<LOG2N>(u, slab, l, lane, false);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) gx[e] = fmaf(u[e], c[e], gx[e]);
+        } else {
+            for (int m = T - 1; m >= 0; --m) {
+                fwht_flip<LOG2N>(u, slab, l, lane, in_a);
+                in_a = !in_a;
+                load16<C::L>(c, Ds + (size_t)m * N);
+                if (m > 0) {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) u[e] *= c[e];
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) gx[e] = fmaf(u[e], c[e], gx[e]);
+                }
             }
         }
     }
