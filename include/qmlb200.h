@@ -121,7 +121,7 @@ int qmlb_fchl19_forward_jacobian(const float *X, const float *Z, const int *atom
  * Within a group rows follow (m,a) order, so the result is deterministic.
  * rows_cap must be >= qmlb_rows_capacity(n_atoms_upper, nelements).  `scratch` is
  * qmlb_group_scratch_bytes(nb, nelements) bytes of device memory. */
-#define QMLB_ROW_TILE 64
+#define QMLB_ROW_TILE 128
 size_t qmlb_rows_capacity(size_t n_atoms_upper, int nelements);
 size_t qmlb_group_scratch_bytes(int nb, int nelements);
 int qmlb_group_by_element(const float *Z, const int *atom_counts, const float *elements, int nelements, int nb,
@@ -155,6 +155,14 @@ int qmlb_group_by_element_noalloc(const float *Z, const int *atom_counts, const 
  * transpose = 1: out = in . P_e^T          (the autograd backward: in is [rows, npcas], out [rows, repsize]) */
 int qmlb_pca_project(const float *in, const float *reductors, const int *group_start, int nelements, size_t rows_cap,
                      int repsize, int npcas, int transpose, float *out, qmlb_stream_t stream);
+
+/* The same contraction on the 5th-generation tensor cores: tcgen05.mma kind::tf32 with the accumulator in tensor
+ * memory and a 3xTF32 operand split (fp32-accurate result).  sub_rows = matrix rows per grouped row (1 for
+ * representations and gradients, 3*A for Jacobians).  qmlb_tc_timeouts() returns how many blocks ever gave up on a
+ * bounded wait (0 in a healthy run; it synchronises the device). */
+int qmlb_pca_project_tc(const float *in, const float *reductors, const int *group_start, int nelements, size_t rows_cap,
+                        int sub_rows, int repsize, int npcas, int transpose, float *out, qmlb_stream_t stream);
+int qmlb_tc_timeouts(void);
 
 /* ---- SORF ----------------------------------------------------------------------------------- */
 

@@ -12,7 +12,7 @@ import torch
 from . import _lib
 from ._lib import FchlParamsC, check
 
-ROW_TILE = 64  # QMLB_ROW_TILE
+ROW_TILE = 128  # QMLB_ROW_TILE
 
 
 def _stream(device):
@@ -179,16 +179,26 @@ def group_by_element(Z, atom_counts, elements, n_atoms_upper=None):
     return Grouping(row_of_slot, slot_of_row, group_start, rows_cap, nel)
 
 
-def pca_project(inp, reductors, grouping, transpose=False, out=None):
+def pca_project(inp, reductors, grouping, transpose=False, out=None, tensor_cores=False):
     nel, repsize, npcas = reductors.shape
     rows = grouping.rows_cap
     width = repsize if transpose else npcas
     if out is None:
         out = torch.empty(rows, width, dtype=torch.float32, device=inp.device)
+    if tensor_cores:
+        check(_lib.load().qmlb_pca_project_tc(_p(inp, torch.float32, 'in'), _p(reductors.contiguous(), torch.float32, 'reductors'),
+                                              _p(grouping.group_start), nel, rows, 1, repsize, npcas, int(bool(transpose)),
+                                              _p(out), _stream(inp.device)), 'qmlb_pca_project_tc')
+        return out
     check(_lib.load().qmlb_pca_project(_p(inp, torch.float32, 'in'), _p(reductors.contiguous(), torch.float32, 'reductors'),
                                        _p(grouping.group_start), nel, rows, repsize, npcas, int(bool(transpose)), _p(out),
                                        _stream(inp.device)), 'qmlb_pca_project')
     return out
+
+
+def tc_timeouts():
+    """Number of tensor-core blocks that ever gave up on a bounded wait (synchronises the device)."""
+    return _lib.load().qmlb_tc_timeouts()
 
 
 def sorf_coefficients(u, D, normalisation, ntransforms):

@@ -11,7 +11,7 @@
 
 namespace {
 
-constexpr int BM = QMLB_ROW_TILE, BN = 64, BK = 16, PAD = 4;
+constexpr int BM = 64, BN = 64, BK = 16, PAD = 4;  // BM divides QMLB_ROW_TILE
 
 template <bool TRANS>
 __global__ void __launch_bounds__(256)

@@ -62,10 +62,11 @@ int predict_pipeline(const float *X, const float *Z, const int *atom_counts, int
     if ((rc = qmlb_group_by_element(Z, atom_counts, elements, nelements, nb, A, row_of_slot, slot_of_row, group_start,
                                     W.rows_cap, base + W.off_scratch, stream))) return rc;
     if ((rc = qmlb_fchl19_forward(X, Z, atom_counts, nb, A, p, cell, inv_cell, row_of_slot, rep, stream))) return rc;
-    if ((rc = qmlb_pca_project(rep, reductors, group_start, nelements, W.rows_cap, repsize, npcas, 0, x, stream))) return rc;
+    // both projections run on the tensor cores (tcgen05, 3xTF32 split: fp32-accurate)
+    if ((rc = qmlb_pca_project_tc(rep, reductors, group_start, nelements, W.rows_cap, 1, repsize, npcas, 0, x, stream))) return rc;
     if ((rc = features(x, group_start, slot_of_row, W.rows_cap, atom_energy, gx))) return rc;
     // the representation buffer is reused for d(energy)/d(representation)
-    if ((rc = qmlb_pca_project(gx, reductors, group_start, nelements, W.rows_cap, repsize, npcas, 1, rep, stream))) return rc;
+    if ((rc = qmlb_pca_project_tc(gx, reductors, group_start, nelements, W.rows_cap, 1, repsize, npcas, 1, rep, stream))) return rc;
     return qmlb_fchl19_backward(X, Z, atom_counts, nb, A, p, cell, inv_cell, row_of_slot, rep, grad_X, atom_energy, energy,
                                 stream);
 }

@@ -14,7 +14,7 @@
 
 namespace {
 
-constexpr int BM = QMLB_ROW_TILE;  // rows per block
+constexpr int BM = 64;             // rows per block (divides QMLB_ROW_TILE, so a block never straddles two elements)
 constexpr int BN = 64;             // features per chunk
 constexpr int XS = BM + 4;         // row stride of the transposed x tile   Xs[k][row]
 constexpr int WS = BN + 1;         // row stride of the W chunk             Wc[k][feature]  (odd: conflict-free columns)

@@ -34,7 +34,7 @@ def test_host_only_entry_points():
     assert lib.qmlb_version() >= 100
     assert lib.qmlb_fchl19_repsize(3, 24, 22) == 336          # FCHL.py:42
     assert lib.qmlb_fchl19_repsize(5, 24, 22) == 780
-    assert lib.qmlb_rows_capacity(1000, 3) % 64 == 0 and lib.qmlb_rows_capacity(1000, 3) >= 1000
+    assert lib.qmlb_rows_capacity(1000, 3) % 128 == 0 and lib.qmlb_rows_capacity(1000, 3) >= 1000
     assert lib.qmlb_sorf_pack_bytes(3, 256, 255, 1) == lib.qmlb_sorf_pack_bytes(3, 256, 256, 1)   # stacks padded to pairs
     assert lib.qmlb_predict_workspace_bytes(10000, 21, 210000, 3, 336, 256) > 210000 * (336 + 512) * 4
     # argument validation happens before any device work

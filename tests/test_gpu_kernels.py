@@ -153,6 +153,29 @@ def test_pca_project_both_directions(cabi, repsize, npcas):
         assert (back[r0:r1] - ref).abs().max() <= 1e-5 * max(1.0, float(ref.abs().max()))
 
 
+@pytest.mark.parametrize('repsize,npcas', [(336, 128), (336, 256), (780, 128), (50, 16), (37, 24)])
+def test_pca_tensor_core_kernel_matches_fp32_reference(cabi, repsize, npcas):
+    """tcgen05 3xTF32 projection against a float64 product, with the fp32 FFMA kernel as the yardstick: the split
+    must keep fp32-level accuracy (a single-pass TF32 product would be ~1e-3)."""
+    X, Z, c, species = H.batch_mixed(30, seed=repsize)
+    el = torch.tensor(species, dtype=torch.float32, device=DEV)
+    g = cabi.group_by_element(Z.to(DEV), c.to(DEV), el)
+    gen = torch.Generator().manual_seed(2)
+    red = torch.randn(len(species), repsize, npcas, generator=gen)
+    inp = torch.randn(g.rows_cap, repsize, generator=gen)
+    gs = g.group_start.cpu()
+    for transpose, src in ((False, inp), (True, torch.randn(g.rows_cap, npcas, generator=gen))):
+        tc = cabi.pca_project(src.to(DEV), red.to(DEV), g, transpose=transpose, tensor_cores=True).cpu().double()
+        ff = cabi.pca_project(src.to(DEV), red.to(DEV), g, transpose=transpose).cpu().double()
+        for ei in range(len(species)):
+            r0, r1 = int(gs[ei]), int(gs[ei + 1])
+            ref = src[r0:r1].double() @ (red[ei].double().T if transpose else red[ei].double())
+            scale = max(1.0, float(ref.abs().max()))
+            assert (ff[r0:r1] - ref).abs().max() <= 3e-6 * scale
+            assert (tc[r0:r1] - ref).abs().max() <= 6e-6 * scale
+    assert cabi.tc_timeouts() == 0
+
+
 @pytest.mark.parametrize('N', [8, 32, 64, 128, 256, 512, 1024, 2048])
 @pytest.mark.parametrize('T', [1, 2, 3])
 def test_sorf_coefficients_and_backward(cabi, N, T):
