@@ -31,7 +31,13 @@ sys.path.insert(0, ROOT)
 
 NPCAS, NSTACKS, SIGMA = 256, 256, 2.0
 SPECIES = [1, 6, 8]
-KERNELS_PER_STEP = 8  # count, scan, assign, fchl forward, pca, sorf fused, pca^T, fchl backward
+# name -> (species, npcas, nstacks, molecules per GPU (c2: in total), description)
+WORKLOADS = {
+    'c1': ([1, 6, 8], 256, 256, 10000, '21-atom C9H8O4 conformers, weak scaling'),
+    'c0': ([1, 6, 8], 128, 128, 1000, '9-atom conformers'),
+    'c2': ([1, 6, 7, 8, 9], 128, 256, 200000, 'mixed molecules with 4-29 atoms, sharded over the ranks (strong scaling)'),
+}
+KERNELS_PER_STEP = 8  # count, scan, assign, fchl forward, pca (tcgen05), sorf fused, pca^T (tcgen05), fchl backward
 
 
 def parse_args():
@@ -40,28 +46,31 @@ def parse_args():
     ap.add_argument('--steps', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--conformers', type=int, default=10000)
+    ap.add_argument('--workload', default='c1', choices=sorted(WORKLOADS))
+    ap.add_argument('--conformers', type=int, default=0, help='molecules per GPU (0 = the workload default)')
     ap.add_argument('--cpu-sample', type=int, default=256, help='conformers per CPU-baseline step')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     return ap.parse_args()
 
 
-def workload(nconf, seed):
+def workload(nconf, seed, name='c1'):
     from qml_lightning_b200.utils import synthetic as syn
-    X, Z, counts = syn.conformers(seed, syn.C1_CHARGES, nconf)
+    if name == 'c2':
+        return syn.mixed_molecules(seed, nconf)
+    X, Z, counts = syn.conformers(seed, syn.C1_CHARGES if name == 'c1' else syn.C0_CHARGES, nconf)
     return X, Z, counts
 
 
-def algorithmic_bytes_per_atom(repsize):
+def algorithmic_bytes_per_atom(repsize, npcas=NPCAS, nstacks=NSTACKS):
     """Inter-stage tensors of the unfused chain written once and read once, plus 40 bytes of input/output."""
-    F = NPCAS * NSTACKS
-    return 4 * (2 * F + 4 * repsize + 4 * NPCAS) + 40
+    F = npcas * nstacks
+    return 4 * (2 * F + 4 * repsize + 4 * npcas) + 40
 
 
-def sorf_kernel_bytes_per_atom():
+def sorf_kernel_bytes_per_atom(npcas=NPCAS, nstacks=NSTACKS):
     """Dominant kernel: coefficient tensor out and back, projected input in, gradient out, atom energy."""
-    F = NPCAS * NSTACKS
-    return 4 * (2 * F + 2 * NPCAS) + 4
+    F = npcas * nstacks
+    return 4 * (2 * F + 2 * npcas) + 4
 
 
 class ClockSampler:
@@ -108,17 +117,20 @@ class ClockSampler:
                 'reasons': sorted(reasons), 'samples': len(sm)}
 
 
-def build_model(device, X, Z, counts):
+def build_model(device, X, Z, counts, species=SPECIES, npcas=NPCAS, nstacks=NSTACKS):
     """Model through the public API: FCHLCuda + HadamardFeaturesModel, reductors from SVD of our own representation."""
     import qml_lightning_b200 as q
     np.random.seed(1234)
     torch.manual_seed(1234)
-    rep = q.FCHLCuda(species=np.array(SPECIES), rcut=6.0, nRs2=24, nRs3=22, eta2=0.32, eta3=2.7, two_body_decay=1.8,
+    rep = q.FCHLCuda(species=np.array(species), rcut=6.0, nRs2=24, nRs3=22, eta2=0.32, eta3=2.7, two_body_decay=1.8,
                      three_body_weight=13.4, three_body_decay=0.57, device=device)
-    model = q.HadamardFeaturesModel(rep=rep, elements=np.array(SPECIES), ntransforms=1, sigma=SIGMA, llambda=1e-5,
-                                    npcas=NPCAS, nstacks=NSTACKS, nbatch_train=64, nbatch_test=len(X))
-    sub = slice(0, 64)
-    model.get_reductors([x for x in X[sub]], [z for z in Z[sub]], npcas=NPCAS, npca_choice=512, nsamples=512, print_info=False)
+    model = q.HadamardFeaturesModel(rep=rep, elements=np.array(species), ntransforms=1, sigma=SIGMA, llambda=1e-5,
+                                    npcas=npcas, nstacks=nstacks, nbatch_train=64, nbatch_test=len(X))
+    nsub = min(len(X), 2048)      # enough atoms of the rarest species for the SVD
+    Xl = [X[i, :counts[i]] for i in range(nsub)]
+    Zl = [Z[i, :counts[i]] for i in range(nsub)]
+    model.nbatch_train = nsub
+    model.get_reductors(Xl, Zl, npcas=npcas, npca_choice=512, nsamples=512, print_info=False)
     model.set_alpha(torch.from_numpy(np.random.default_rng(5).normal(size=model.nfeatures()).astype(np.float32)))
     return rep, model
 
@@ -184,20 +196,31 @@ def main():
         dist.init_process_group('nccl', device_id=dev)
 
     from qml_lightning_b200 import cabi
-    X, Z, counts = workload(args.conformers, 1001 + rank)       # every rank owns its own molecules
-    rep, model = build_model(dev, X, Z, counts)
+    from qml_lightning_b200.utils.sharding import my_shard
+    species, npcas, nstacks, default_n, _ = WORKLOADS[args.workload]
+    nreq = args.conformers or default_n
+    if args.workload == 'c2':
+        # one global batch, contiguous atom-balanced shards (strong scaling)
+        X, Z, counts = workload(nreq, 1002, 'c2')
+        lo, hi = my_shard(counts, rank, world)
+        X, Z, counts = X[lo:hi], Z[lo:hi], counts[lo:hi]
+        nglobal = nreq
+    else:
+        X, Z, counts = workload(nreq, 1001 + rank, args.workload)       # every rank owns its own molecules
+        nglobal = nreq * world
+    rep, model = build_model(dev, X, Z, counts, species, npcas, nstacks)
     nconf, A = Z.shape
     natoms = int(counts.sum())
     kp = rep.kernel_params(dev)
     Xd, Zd, cd = (torch.from_numpy(a).to(dev) for a in (X, Z, counts))
-    atomIDs = torch.arange(A, dtype=torch.int32, device=dev).repeat(nconf)
-    molIDs = torch.arange(nconf, dtype=torch.int32, device=dev).repeat_interleave(A)
+    atomIDs = torch.from_numpy(np.concatenate([np.arange(n, dtype=np.int32) for n in counts])).to(dev)
+    molIDs = torch.from_numpy(np.repeat(np.arange(nconf, dtype=np.int32), counts)).to(dev)
     flush = torch.empty(512 * 1024 * 1024, dtype=torch.uint8, device=dev)   # > 126 MB L2
     E = torch.empty(nconf, dtype=torch.float32, device=dev)
     G = torch.empty(nconf, A, 3, dtype=torch.float32, device=dev)
 
     def step():
-        cabi.sorf_predict(Xd, Zd, cd, kp, model.species, model.reductors, model.packed, NSTACKS, 1, SIGMA,
+        cabi.sorf_predict(Xd, Zd, cd, kp, model.species, model.reductors, model.packed, nstacks, 1, SIGMA,
                           n_atoms_upper=natoms, fast_math=model.fast_math, energy=E, grad_X=G)
 
     for _ in range(args.warmup):
@@ -224,7 +247,7 @@ def main():
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_max = float(t.item())
-    value = world * nconf / (ms_max * 1e-3)
+    value = nglobal / (ms_max * 1e-3)
 
     # ---- dominant kernel alone, CUDA events on the launching stream -------------------------------------------------
     g = cabi.group_by_element(Zd, cd, model.species, natoms)
@@ -232,7 +255,7 @@ def main():
     cabi.fchl19_forward(Xd, Zd, cd, kp, row_of_slot=g.row_of_slot, out=repbuf)
     xproj = cabi.pca_project(repbuf, model.reductors, g)
     def sorf_alone():
-        cabi.sorf_energy_grad(xproj, g, model.packed, NPCAS, NSTACKS, 1, SIGMA, model.fast_math)
+        cabi.sorf_energy_grad(xproj, g, model.packed, npcas, nstacks, 1, SIGMA, model.fast_math)
 
     for _ in range(3):          # warm-up: also lets the caching allocator keep the output blocks
         sorf_alone()
@@ -275,7 +298,7 @@ def main():
     t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_value = world * nconf / (float(t.item()) * 1e-3)
+    e2e_value = nglobal / (float(t.item()) * 1e-3)
 
     if rank != 0:
         if dist is not None:
@@ -289,27 +312,29 @@ def main():
             peaks = json.load(fh)
         peak_src = 'measured'
     hbm = float(peaks.get('hbm_gbs', 6650.0))
-    k_bytes = sorf_kernel_bytes_per_atom() * natoms
+    k_bytes = sorf_kernel_bytes_per_atom(npcas, nstacks) * natoms
     achieved = k_bytes / (k_ms * 1e-3) / 1e9
-    pipe_bytes = algorithmic_bytes_per_atom(rep.get_repsize()) * natoms * world
+    pipe_bytes = algorithmic_bytes_per_atom(rep.get_repsize(), npcas, nstacks) * natoms * world
     pipe_gbs = pipe_bytes / (ms_max * 1e-3) / 1e9
     line = {
         'metric': 'energy+force predictions', 'value': value, 'unit': 'molecules/s', 'n_gpus': world, 'steps': args.steps,
-        'warmup': args.warmup, 'ms_per_step': ms_max, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+        'warmup': args.warmup, 'ms_per_step': ms_max, 'higher_is_better': True,
+        'scaling': 'strong' if args.workload == 'c2' else 'weak', 'vs_baseline': None,
         'dtype': 'f32', 'data': 'synthetic',
-        'config': {'workload': 'c1', 'molecules_per_gpu': nconf, 'atoms_per_molecule': A, 'species': SPECIES, 'npcas': NPCAS,
-                   'nstacks': NSTACKS, 'features': NPCAS * NSTACKS, 'parallelism': f'molecule shards x{world}, no collective',
+        'config': {'workload': args.workload, 'molecules_per_gpu': nconf, 'atoms_per_molecule': A if args.workload != 'c2' else 'ragged 4-29 (padded to 29)',
+                   'species': species, 'npcas': npcas, 'nstacks': nstacks, 'features': npcas * nstacks,
+                   'parallelism': f'molecule shards x{world}, no collective',
                    'l2': 'flushed between steps (512 MB write outside the timed events); per-step workspace > L2',
                    'fast_math': bool(model.fast_math)},
         'e2e': {'value': e2e_value, 'unit': 'molecules/s', 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h},
         'gpu_launches': KERNELS_PER_STEP * args.steps,
         'clocks': clocks,
         'roofline': {'bound': 'hbm', 'kernel': 'sorf_energy_grad_kernel', 'achieved': achieved, 'peak': hbm, 'unit': 'GB/s',
-                     'frac': achieved / hbm, 'traffic': SORF_KERNEL_DRAM_BYTES_PER_ATOM * natoms if SORF_KERNEL_DRAM_BYTES_PER_ATOM else None,
+                     'frac': achieved / hbm, 'traffic': SORF_KERNEL_DRAM_BYTES_PER_ATOM * natoms if (SORF_KERNEL_DRAM_BYTES_PER_ATOM and args.workload == 'c1') else None,
                      'peak_source': peak_src, 'kernel_ms': k_ms, 'algorithmic_bytes_per_launch': k_bytes,
                      'pipeline_hbm_equivalent_gbs': pipe_gbs / world, 'pipeline_frac': pipe_gbs / world / hbm},
     }
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and args.workload == 'c1':
         rate, dt = cpu_oracle_rate(model, rep, X, Z, counts, args.cpu_sample)
         line['cpu_baseline'] = {'value': rate, 'unit': 'molecules/s', 'cores': os.cpu_count(), 'kind': 'port',
                                 'sample': f'{args.cpu_sample} conformers of the c1 workload, torch CPU fp32 oracle, {dt:.1f} s'}

@@ -16,9 +16,10 @@
 //   * after the last commit the four warps read their 32 accumulator lanes with tcgen05.ld and store the tile.
 // The tensor core adds into its fp32 accumulator with truncation, about one ulp of the running sum per MMA and
 // always towards zero, so a long K loop accumulates a bias (measured 3.5x the error of an fp32 FFMA loop at K = 336).
-// The K loop is therefore cut into groups of GROUP_CHUNKS chunks: every group starts a fresh accumulator in tensor
-// memory and is added to per-thread fp32 registers (round to nearest) when it completes, which keeps the running sums
-// small where the truncation happens.
+// For the projection the K loop is therefore cut into groups of FWD_GROUP_CHUNKS chunks: every group starts a fresh
+// accumulator in tensor memory and is added to per-thread fp32 registers (round to nearest) when it completes, which
+// keeps the running sums small where the truncation happens (measured: below the FFMA loop's error).  The
+// transposed product has a short K (npcas) and feeds only the force chain rule; it accumulates in one go.
 // Every wait is bounded; on a time-out the block records it in a device counter (qmlb_tc_timeouts), skips its
 // stores, releases its tensor memory and returns.
 #include "common.cuh"
@@ -31,7 +32,10 @@ constexpr int STAGE_FLOATS = 4 * TILE_FLOATS;         // A_hi, A_lo, B_hi, B_lo
 constexpr uint32_t LBO_BYTES = BM * 16;               // next 4-element K chunk of the same rows
 constexpr uint32_t SBO_BYTES = 128;                   // next 8-row group
 constexpr int WAIT_LIMIT = 1 << 22;
-constexpr int GROUP_CHUNKS = 3;                       // K = 48 per tensor-memory accumulation group
+#ifndef QMLB_FWD_GROUP_CHUNKS
+#define QMLB_FWD_GROUP_CHUNKS 2
+#endif
+constexpr int FWD_GROUP_CHUNKS = QMLB_FWD_GROUP_CHUNKS;  // projection: K = 32 per tensor-memory accumulation group
 
 __device__ int g_tc_timeouts = 0;
 
@@ -85,7 +89,10 @@ __device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
 // element (row r, k) of an operand tile in the canonical layout, as a float offset
 __device__ __forceinline__ int tile_offset(int r, int k) { return (k >> 2) * (BM * 4) + (r >> 3) * 32 + (r & 7) * 4 + (k & 3); }
 
-template <bool TRANS>
+// GROUP_CHUNKS > 0: flush the tensor-memory accumulator into registers every GROUP_CHUNKS chunks (used for the
+// projection, whose result feeds cos()); GROUP_CHUNKS == 0: one accumulation over all of K (used for the transposed
+// product, whose K = npcas is short and whose result only feeds the force chain rule).
+template <bool TRANS, int GROUP_CHUNKS>
 __global__ void __launch_bounds__(128)
 pca_tc_kernel(const float *__restrict__ in, const float *__restrict__ P, const int *__restrict__ group_start, int nel, int K,
               int Nout, int npcas, size_t p_stride, int sub_rows, float *__restrict__ out) {
@@ -120,62 +127,77 @@ pca_tc_kernel(const float *__restrict__ in, const float *__restrict__ P, const i
     const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     const int nchunks = (K + BK - 1) / BK;
     bool ok = true;
-    float racc[BN];  // this thread's output row (lane of the accumulator), summed over the K groups in fp32
+    constexpr bool GROUPED = GROUP_CHUNKS > 0;
+    constexpr int GC = GROUPED ? GROUP_CHUNKS : 1;
+    float racc[GROUPED ? BN : 1];  // this thread's output row (lane of the accumulator), summed over the K groups in fp32
 #pragma unroll
-    for (int i = 0; i < BN; ++i) racc[i] = 0.f;
+    for (int i = 0; i < (GROUPED ? BN : 1); ++i) racc[i] = 0.f;
     uint32_t phase[STAGES] = {0u, 0u};  // parity of the next completion of each stage barrier
+
+    // Register prefetch: the global loads of chunk c+1 are issued before chunk c is handed to the tensor core, so
+    // their latency overlaps the barrier, the MMA issue and the next stage wait.
+    float4 ra[BK / 4];
+    float rb[BK];
+    auto fetch = [&](int c) {
+        const int k0 = c * BK;
+        const float *src = in + (size_t)(row0 + tid) * K + k0;
+#pragma unroll
+        for (int q = 0; q < BK / 4; ++q) {
+            if ((K & 3) == 0 && k0 + 4 * q + 3 < K) {
+                ra[q] = *reinterpret_cast<const float4 *>(src + 4 * q);
+            } else {
+                float v[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[i] = (k0 + 4 * q + i < K) ? src[4 * q + i] : 0.f;
+                ra[q] = make_float4(v[0], v[1], v[2], v[3]);
+            }
+        }
+        const int n = col0 + tid;
+        if (TRANS && (npcas & 3) == 0 && n < Nout && k0 + BK <= K) {
+            // B[n][k] = P[n][k]: the thread's 16 values are contiguous
+            const float4 *bsrc = reinterpret_cast<const float4 *>(Pe + (size_t)n * npcas + k0);
+#pragma unroll
+            for (int q = 0; q < BK / 4; ++q) {
+                const float4 t = __ldg(bsrc + q);
+                rb[4 * q] = t.x; rb[4 * q + 1] = t.y; rb[4 * q + 2] = t.z; rb[4 * q + 3] = t.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < BK; ++i) {
+                const int k = k0 + i;
+                rb[i] = (n < Nout && k < K) ? (TRANS ? Pe[(size_t)n * npcas + k] : Pe[(size_t)k * npcas + n]) : 0.f;
+            }
+        }
+    };
+    fetch(0);
 
     for (int c = 0; c < nchunks; ++c) {
         const int s = c & 1;
         float *stage = smem + (size_t)s * STAGE_FLOATS;
-        const bool group_start_chunk = (c % GROUP_CHUNKS) == 0;
-        const bool group_end_chunk = ((c + 1) % GROUP_CHUNKS) == 0 || c == nchunks - 1;
+        const bool group_start_chunk = GROUPED ? (c % GC) == 0 : c == 0;
+        const bool group_end_chunk = (GROUPED && ((c + 1) % GC) == 0) || c == nchunks - 1;
         // The MMAs that read this stage two chunks ago must have completed, unless a group flush already waited
         // for everything issued so far.
-        if (c >= STAGES && ((c - 1) % GROUP_CHUNKS) != GROUP_CHUNKS - 1 && ((c - 2) % GROUP_CHUNKS) != GROUP_CHUNKS - 1) {
+        if (c >= STAGES && (!GROUPED || (((c - 1) % GC) != GC - 1 && ((c - 2) % GC) != GC - 1))) {
             if (!mbar_wait(smem_u32(&bars[s]), phase[s])) ok = false;
             phase[s] ^= 1u;
         }
-        const int k0 = c * BK;
-        // A: thread = row, 4 float4 along K (rows beyond the data are element-group padding: still allocated)
-        {
-            const float *src = in + (size_t)(row0 + tid) * K + k0;
+        // split the prefetched operands and store them in the canonical layout (thread = A row = B column)
 #pragma unroll
-            for (int q = 0; q < BK / 4; ++q) {
-                float v[4];
-                if ((K & 3) == 0 && k0 + 4 * q + 3 < K) {
-                    const float4 t = *reinterpret_cast<const float4 *>(src + 4 * q);
-                    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-                } else {
+        for (int q = 0; q < BK / 4; ++q) {
+            const float v[4] = {ra[q].x, ra[q].y, ra[q].z, ra[q].w};
+            float hi[4], lo[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) v[i] = (k0 + 4 * q + i < K) ? src[4 * q + i] : 0.f;
-                }
-                float hi[4], lo[4];
+            for (int i = 0; i < 4; ++i) split_tf32(v[i], hi[i], lo[i]);
+            const int off = tile_offset(tid, 4 * q);
+            *reinterpret_cast<float4 *>(stage + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<float4 *>(stage + TILE_FLOATS + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) split_tf32(v[i], hi[i], lo[i]);
-                const int off = tile_offset(tid, 4 * q);
-                *reinterpret_cast<float4 *>(stage + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
-                *reinterpret_cast<float4 *>(stage + TILE_FLOATS + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
-            }
+            for (int i = 0; i < 4; ++i) split_tf32(rb[4 * q + i], hi[i], lo[i]);
+            *reinterpret_cast<float4 *>(stage + 2 * TILE_FLOATS + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<float4 *>(stage + 3 * TILE_FLOATS + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
         }
-        // B: thread = output column n
-        {
-            const int n = col0 + tid;
-#pragma unroll
-            for (int q = 0; q < BK / 4; ++q) {
-                float hi[4], lo[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int k = k0 + 4 * q + i;
-                    float v = 0.f;
-                    if (n < Nout && k < K) v = TRANS ? Pe[(size_t)n * npcas + k] : Pe[(size_t)k * npcas + n];
-                    split_tf32(v, hi[i], lo[i]);
-                }
-                const int off = tile_offset(tid, 4 * q);
-                *reinterpret_cast<float4 *>(stage + 2 * TILE_FLOATS + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
-                *reinterpret_cast<float4 *>(stage + 3 * TILE_FLOATS + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
-            }
-        }
+        if (c + 1 < nchunks) fetch(c + 1);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the MMA unit
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
@@ -199,12 +221,50 @@ pca_tc_kernel(const float *__restrict__ in, const float *__restrict__ P, const i
             if (!mbar_wait(smem_u32(&bars[s]), phase[s])) ok = false;
             phase[s] ^= 1u;
             // the other stage's last commit (if any since its last wait) has completed too: consume its phase
-            if (c >= 1 && ((c - 1) % GROUP_CHUNKS) != GROUP_CHUNKS - 1) {
+            if (c >= 1 && (!GROUPED || ((c - 1) % GC) != GC - 1)) {
                 if (!mbar_wait(smem_u32(&bars[s ^ 1]), phase[s ^ 1])) ok = false;
                 phase[s ^ 1] ^= 1u;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (GROUPED) {
 #pragma unroll
+                for (int cc = 0; cc < BN; cc += 16) {
+                    uint32_t v[16];
+                    const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)cc;
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                        : "r"(taddr));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) racc[cc + i] += __uint_as_float(v[i]);
+                }
+                // the next group's first MMA overwrites the accumulator: order it after these loads
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncthreads();
+            }
+        }
+    }
+    if (!ok) failed = 1;  // benign race: every writer stores 1
+    __syncthreads();
+
+    if (!failed) {
+        const long r = row0 + warp * 32 + lane;
+        float *dst = out + (size_t)r * Nout + col0;
+        const bool full = col0 + BN <= Nout && (Nout & 3) == 0;
+        if (GROUPED) {
+            if (full) {
+#pragma unroll
+                for (int cc = 0; cc < BN; cc += 4)
+                    *reinterpret_cast<float4 *>(dst + cc) = make_float4(racc[cc], racc[cc + 1], racc[cc + 2], racc[cc + 3]);
+            } else {
+#pragma unroll
+                for (int cc = 0; cc < BN; ++cc)
+                    if (col0 + cc < Nout) dst[cc] = racc[cc];
+            }
+        } else {
+#pragma unroll 1
             for (int cc = 0; cc < BN; cc += 16) {
                 uint32_t v[16];
                 const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)cc;
@@ -214,28 +274,18 @@ pca_tc_kernel(const float *__restrict__ in, const float *__restrict__ P, const i
                       "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
                     : "r"(taddr));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (full) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) racc[cc + i] += __uint_as_float(v[i]);
+                    for (int q = 0; q < 4; ++q)
+                        *reinterpret_cast<float4 *>(dst + cc + 4 * q) =
+                            make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]),
+                                        __uint_as_float(v[4 * q + 3]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        if (col0 + cc + i < Nout) dst[cc + i] = __uint_as_float(v[i]);
+                }
             }
-            // the next group's first MMA overwrites the accumulator: order it after these loads
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncthreads();
-        }
-    }
-    if (!ok) failed = 1;  // benign race: every writer stores 1
-    __syncthreads();
-
-    if (!failed) {
-        const long r = row0 + warp * 32 + lane;
-        float *dst = out + (size_t)r * Nout + col0;
-        if (col0 + BN <= Nout && (Nout & 3) == 0) {
-#pragma unroll
-            for (int cc = 0; cc < BN; cc += 4)
-                *reinterpret_cast<float4 *>(dst + cc) = make_float4(racc[cc], racc[cc + 1], racc[cc + 2], racc[cc + 3]);
-        } else {
-#pragma unroll
-            for (int cc = 0; cc < BN; ++cc)
-                if (col0 + cc < Nout) dst[cc] = racc[cc];
         }
     } else if (tid == 0) {
         atomicAdd(&g_tc_timeouts, 1);
@@ -268,12 +318,12 @@ extern "C" int qmlb_pca_project_tc(const float *in, const float *reductors, cons
     const size_t smem = sizeof(float) * STAGES * STAGE_FLOATS + 128;
     const size_t p_stride = (size_t)repsize * npcas;
     if (transpose) {
-        if (int rc = qmlb::ensure_smem(pca_tc_kernel<true>, smem, "qmlb_pca_project_tc")) return rc;
-        pca_tc_kernel<true><<<grid, 128, smem, qmlb::as_stream(stream)>>>(in, reductors, group_start, nelements, K, Nout, npcas,
+        if (int rc = qmlb::ensure_smem(pca_tc_kernel<true, 0>, smem, "qmlb_pca_project_tc")) return rc;
+        pca_tc_kernel<true, 0><<<grid, 128, smem, qmlb::as_stream(stream)>>>(in, reductors, group_start, nelements, K, Nout, npcas,
                                                                         p_stride, sub_rows, out);
     } else {
-        if (int rc = qmlb::ensure_smem(pca_tc_kernel<false>, smem, "qmlb_pca_project_tc")) return rc;
-        pca_tc_kernel<false><<<grid, 128, smem, qmlb::as_stream(stream)>>>(in, reductors, group_start, nelements, K, Nout, npcas,
+        if (int rc = qmlb::ensure_smem(pca_tc_kernel<false, FWD_GROUP_CHUNKS>, smem, "qmlb_pca_project_tc")) return rc;
+        pca_tc_kernel<false, FWD_GROUP_CHUNKS><<<grid, 128, smem, qmlb::as_stream(stream)>>>(in, reductors, group_start, nelements, K, Nout, npcas,
                                                                          p_stride, sub_rows, out);
     }
     return qmlb::check_launch("qmlb_pca_project_tc");

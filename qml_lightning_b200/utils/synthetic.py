@@ -38,16 +38,29 @@ def conformers(seed, charges, nconf, jitter=0.05, dmax=1.5):
 
 
 def mixed_molecules(seed, nmol, min_atoms=4, max_atoms=29, species=(1, 6, 7, 8, 9), probs=(0.5, 0.3, 0.1, 0.08, 0.02)):
-    """Zero-padded batch of random clusters with atom counts uniform in [min_atoms, max_atoms]."""
+    """Zero-padded batch of random clusters with atom counts uniform in [min_atoms, max_atoms].
+
+    Same construction as ``random_cluster`` (atom k at U(1.0,1.6) from a random earlier atom, rejected below 1.0 from
+    any atom), vectorised over the molecules so that 200,000 molecules take seconds.
+    """
     rng = np.random.default_rng(seed)
     counts = rng.integers(min_atoms, max_atoms + 1, size=nmol).astype(np.int32)
-    X = np.zeros((nmol, max_atoms, 3), dtype=np.float32)
+    X = np.zeros((nmol, max_atoms, 3), dtype=np.float64)
     Z = np.zeros((nmol, max_atoms), dtype=np.float32)
-    for m in range(nmol):
-        n = int(counts[m])
-        X[m, :n] = random_cluster(rng, n, 1.0, 1.6)
-        Z[m, :n] = rng.choice(species, size=n, p=probs)
-    return X, Z, counts
+    for k in range(1, max_atoms):
+        todo = np.where(counts > k)[0]
+        while todo.size:
+            parent = (rng.random(todo.size) * k).astype(np.int64)
+            v = rng.normal(size=(todo.size, 3))
+            v /= np.linalg.norm(v, axis=1, keepdims=True)
+            cand = X[todo, parent] + v * rng.uniform(1.0, 1.6, size=(todo.size, 1))
+            d = np.linalg.norm(X[todo, :k] - cand[:, None, :], axis=2).min(axis=1)
+            ok = d >= 1.0
+            X[todo[ok], k] = cand[ok]
+            todo = todo[~ok]
+    real = np.arange(max_atoms)[None, :] < counts[:, None]
+    Z[real] = rng.choice(np.asarray(species, dtype=np.float32), size=int(real.sum()), p=probs)
+    return X.astype(np.float32), Z, counts
 
 
 def sorf_parameters(seed, nelements, npcas, nstacks, ntransforms=1):
