@@ -260,6 +260,17 @@ int qmlb_sorf_train_features(const float *x, const float *dx, const float *Dmat,
                              int A, size_t rows_cap, int N, int S, int T, float sigma, double *Zout, double *G,
                              float *sinc_scratch, qmlb_stream_t stream);
 
+/* RFF training features of one batch: random_fourrier_features_kernel / _derivative
+ * (cuda/random_features_kernel.cu:5-94) via get_rff / get_rff_derivatives (cuda/random_features.cpp:11-33), as
+ * driven by RandomFourrierFeaturesModel.calculate_features (models/random_features.py:60-67), for all elements
+ * at once.  x f32[rows_cap,K], dx f32[rows_cap,A,3,K] element-grouped; W f32[nel,K,D], b f32[nel,D].
+ * Zout f64[nb,D], G f64[nb,A,3,D] (= -dZ/dr) overwritten.  arg_scratch: rows_cap*D floats; t_scratch:
+ * rows_cap*A*3*D floats (NULL together with dx and G for energy-only training). */
+int qmlb_rff_train_features(const float *x, const float *dx, const float *W, const float *b, const int *group_start,
+                            const int *slot_of_row, const int *row_of_slot, const int *atom_counts, int nelements, int nb,
+                            int A, size_t rows_cap, int K, int D, double *Zout, double *G, float *arg_scratch,
+                            float *t_scratch, qmlb_stream_t stream);
+
 /* ZTZ += M^T M (row-major UPPER triangle only) and ZTy += M^T y for a row block M f64[rows,F]:
  * torch.matmul(Ztrain.T, Ztrain) / torch.matmul(Ztrain.T, targets) in build_Z_components (models/kernel.py:172-192).
  * cuBLAS DSYRK + DGEMV on `stream`.  qmlb_symmetrize_upper mirrors the triangle before the solve. */

@@ -59,6 +59,8 @@ SIGNATURES = {
     'qmlb_sorf_train_features': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                          c_int, c_int, c_size_t, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p,
                                          c_void_p]),
+    'qmlb_rff_train_features': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                        c_int, c_size_t, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     'qmlb_normal_equations_accumulate': (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     'qmlb_symmetrize_upper': (c_int, [c_void_p, c_int, c_void_p]),
 }

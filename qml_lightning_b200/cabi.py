@@ -400,3 +400,20 @@ def normal_equations_accumulate(M, y, ZTZ, ZTy):
 
 def symmetrize_upper(ZTZ):
     check(_lib.load().qmlb_symmetrize_upper(_p(ZTZ, torch.float64, 'ZTZ'), ZTZ.shape[0], _stream(ZTZ.device)), 'qmlb_symmetrize_upper')
+
+
+def rff_train_features(x, dx, W, b, grouping, atom_counts, nb, A):
+    """RFF per-molecule features ``Z f64[nb,D]`` and force features ``G f64[nb,A,3,D]`` (``None`` without ``dx``)."""
+    nel, K, D = W.shape
+    dev = x.device
+    Z = torch.empty(nb, D, dtype=torch.float64, device=dev)
+    G = torch.empty(nb, A, 3, D, dtype=torch.float64, device=dev) if dx is not None else None
+    arg = torch.empty(grouping.rows_cap, D, dtype=torch.float32, device=dev)
+    T = torch.empty(grouping.rows_cap, A, 3, D, dtype=torch.float32, device=dev) if dx is not None else None
+    check(_lib.load().qmlb_rff_train_features(_p(x, torch.float32, 'x'), _p(dx, torch.float32, 'dx'), _p(W.contiguous(), torch.float32, 'W'),
+                                              _p(b.contiguous(), torch.float32, 'b'), _p(grouping.group_start),
+                                              _p(grouping.slot_of_row), _p(grouping.row_of_slot),
+                                              _p(atom_counts.contiguous(), torch.int32, 'atom_counts'), nel, nb, A,
+                                              grouping.rows_cap, K, D, _p(Z), _p(G), _p(arg), _p(T), _stream(dev)),
+          'qmlb_rff_train_features')
+    return Z, G

@@ -40,6 +40,28 @@ class RandomFourrierFeaturesModel(BaseKernel, torch.nn.Module):
         self.alpha = alpha.to(self.device)
         self.is_trained = True
 
+    # ---- training ------------------------------------------------------------------------------------------------
+    def training_rows(self, data, with_forces):
+        """Per-molecule features and force features of one formatted batch (upstream calculate_features :60-67 applied
+        to all elements at once)."""
+        X, Zc, counts = data['coordinates'], data['charges'], data['natom_counts']
+        nb, A = Zc.shape
+        kp = self.rep.kernel_params(X.device)
+        g = cabi.group_by_element(Zc, counts, self.species, data['atomIDs'].shape[0])
+        if with_forces:
+            rep_rows, jac_rows = cabi.fchl19_forward_jacobian(X, Zc, counts, kp, data['cells'], data['inv_cells'], grouping=g)
+            dx = cabi.pca_project_jacobian(jac_rows, self.reductors, g)
+            del jac_rows
+        else:
+            rep_rows = torch.zeros(g.rows_cap, self.rep.get_repsize(), dtype=torch.float32, device=X.device)
+            cabi.fchl19_forward(X, Zc, counts, kp, data['cells'], data['inv_cells'], row_of_slot=g.row_of_slot, out=rep_rows)
+            dx = None
+        x = cabi.pca_project(rep_rows, self.reductors, g)
+        return cabi.rff_train_features(x, dx, self.W, self.b, g, counts, nb, A)
+
+    def _parameters_changed(self):
+        pass
+
     # ---- inference -----------------------------------------------------------------------------------------------
     def forward(self, X, Z, atomIDs, molIDs, atom_counts, cell=torch.empty(0, 3, 3), inv_cell=torch.empty(0, 3, 3)):
         """Energies ``[nbatch]`` (no self energies); differentiable with respect to ``X`` (upstream :69-102)."""
