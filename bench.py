@@ -36,6 +36,7 @@ WORKLOADS = {
     'c1': ([1, 6, 8], 256, 256, 10000, '21-atom C9H8O4 conformers, weak scaling'),
     'c0': ([1, 6, 8], 128, 128, 1000, '9-atom conformers'),
     'c2': ([1, 6, 7, 8, 9], 128, 256, 200000, 'mixed molecules with 4-29 atoms, sharded over the ranks (strong scaling)'),
+    'c4': ([1, 6, 8], 256, 128, 512, 'training normal equations: Z^T Z (fp64, 32768^2) over 21-atom conformers, 64 rows each'),
 }
 KERNELS_PER_STEP = 8  # count, scan, assign, fchl forward, pca (tcgen05), sorf fused, pca^T (tcgen05), fchl backward
 
@@ -178,6 +179,54 @@ def run_reference(args, rank, world):
     print(json.dumps(line))
 
 
+def run_training(args, rank, world, local):
+    """c4: normal-equation accumulation over a bounded number of conformers per rank (the full configuration has
+    50,000; the cost is linear in the conformers), one all-reduce of the partial sums at the end."""
+    dev = torch.device('cuda', local)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group('nccl', device_id=dev)
+    species, npcas, nstacks, default_n, _ = WORKLOADS['c4']
+    n = args.conformers or default_n
+    X, Z, counts = workload(n, 1004 + rank, 'c1')
+    rep, model = build_model(dev, X, Z, counts, species, npcas, nstacks)
+    model.nbatch_train = 64
+    rng = np.random.default_rng(7)
+    Xl, Zl = [x for x in X], [z for z in Z]
+    E = rng.normal(size=n)
+    Fl = [rng.normal(size=(21, 3)) for _ in range(n)]
+    model.build_Z_components(Xl[:64], Zl[:64], E[:64], Fl[:64], print_info=False)     # warm-up (cuBLAS handle, allocator)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    t0 = time.perf_counter()
+    ZTZ, ZTy = model.build_Z_components(Xl, Zl, E, Fl, print_info=False)
+    torch.cuda.synchronize()
+    t_acc = time.perf_counter() - t0
+    t1 = time.perf_counter()
+    model.allreduce_normal_equations(ZTZ, ZTy)
+    torch.cuda.synchronize()
+    t_red = time.perf_counter() - t1
+    tt = torch.tensor([t_acc, t_red], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        F = npcas * nstacks
+        t_acc, t_red = float(tt[0]), float(tt[1])
+        flops = 2.0 * 64 * F * F * n * world          # algorithmic: full Z^T Z product per conformer
+        print(json.dumps({
+            'metric': 'normal-equation accumulation', 'value': n * world / t_acc, 'unit': 'conformers/s', 'n_gpus': world,
+            'steps': 1, 'warmup': 1, 'ms_per_step': t_acc * 1e3, 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+            'dtype': 'f64', 'data': 'synthetic',
+            'config': {'workload': 'c4', 'conformers_per_gpu': n, 'rows_per_conformer': 64, 'features': F, 'nbatch_train': 64},
+            'fp64_algorithmic_tflops': flops / t_acc / 1e12, 'allreduce_ms': t_red * 1e3,
+            'allreduce_bytes': int(ZTZ.numel() * 8 + ZTy.numel() * 8)}))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get('RANK', 0))
@@ -185,6 +234,9 @@ def main():
     local = int(os.environ.get('LOCAL_RANK', 0))
     if args.impl == 'reference':
         run_reference(args, rank, world)
+        return
+    if args.workload == 'c4':
+        run_training(args, rank, world, local)
         return
     if not torch.cuda.is_available():
         raise SystemExit('bench.py needs a CUDA device: the prediction path has no CPU fallback')
