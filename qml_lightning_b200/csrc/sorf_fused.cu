@@ -109,6 +109,48 @@ struct Xpose {
     }
 };
 
+// Several independent vectors (one per atom handled by the lane) through one pair of warp barriers.
+template <int LOG2N, int ATOMS>
+struct XposeN {
+    using X = Xpose<LOG2N>;
+    using C = Cfg<LOG2N>;
+    __device__ static __forceinline__ void a_to_b(float (&u)[ATOMS][16], float *slab, int l) {
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a) {
+            float4 *w = reinterpret_cast<float4 *>(slab + a * C::WARP_FLOATS + X::a_base(l));
+#pragma unroll
+            for (int q = 0; q < 4; ++q) w[q] = make_float4(u[a][4 * q], u[a][4 * q + 1], u[a][4 * q + 2], u[a][4 * q + 3]);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a) {
+            const float *r = slab + a * C::WARP_FLOATS + X::b_base(l);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) u[a][e] = r[X::b_const(e)];
+        }
+        __syncwarp();
+    }
+    __device__ static __forceinline__ void b_to_a(float (&u)[ATOMS][16], float *slab, int l) {
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a) {
+            float *w = slab + a * C::WARP_FLOATS + X::b_base(l);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) w[X::b_const(e)] = u[a][e];
+        }
+        __syncwarp();
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a) {
+            const float4 *r = reinterpret_cast<const float4 *>(slab + a * C::WARP_FLOATS + X::a_base(l));
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 t = r[q];
+                u[a][4 * q] = t.x; u[a][4 * q + 1] = t.y; u[a][4 * q + 2] = t.z; u[a][4 * q + 3] = t.w;
+            }
+        }
+        __syncwarp();
+    }
+};
+
 // butterfly across lanes l and l^16 (only N = 512)
 __device__ __forceinline__ void lane16_stage(float (&u)[16], int lane) {
     const float sgn = (lane & 16) ? -1.0f : 1.0f;
@@ -154,6 +196,35 @@ __device__ __forceinline__ void load16(float (&v)[16], const float *p) {
 }
 
 // natural (row) order: 16 consecutive floats per lane
+template <int LOG2N, int ATOMS>
+__device__ __forceinline__ void fwht_flip_n(float (&u)[ATOMS][16], float *slab, int l, int lane, bool from_a) {
+    using C = Cfg<LOG2N>;
+    if (C::LB == 0) {
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a) fwht_regs<4>(u[a]);
+        return;
+    }
+    if (from_a) {
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a) fwht_regs<4>(u[a]);
+        XposeN<LOG2N, ATOMS>::a_to_b(u, slab, l);
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a) {
+            fwht_regs<C::LBT>(u[a]);
+            if (C::LB == 5) lane16_stage(u[a], lane);
+        }
+    } else {
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a) {
+            if (C::LB == 5) lane16_stage(u[a], lane);
+            fwht_regs<C::LBT>(u[a]);
+        }
+        XposeN<LOG2N, ATOMS>::b_to_a(u, slab, l);
+#pragma unroll
+        for (int a = 0; a < ATOMS; ++a) fwht_regs<4>(u[a]);
+    }
+}
+
 __device__ __forceinline__ void load16_row(float (&v)[16], const float *p) {
     const float4 *q = reinterpret_cast<const float4 *>(p);
 #pragma unroll
@@ -163,8 +234,8 @@ __device__ __forceinline__ void load16_row(float (&v)[16], const float *p) {
     }
 }
 
-template <int LOG2N, bool FAST, int TT>
-__global__ void __launch_bounds__(WARPS * 32, SORF_MINB)
+template <int LOG2N, bool FAST, int TT, int ATOMS>
+__global__ void __launch_bounds__(WARPS * 32, ATOMS == 1 ? SORF_MINB : 3)
 sorf_energy_grad_kernel(const float *__restrict__ x, const int *__restrict__ group_start,
                         const int *__restrict__ slot_of_row, int nel, int S, int T_rt, float scale,
                         const float *__restrict__ Dp, const float *__restrict__ bp, const float *__restrict__ ap,
@@ -175,22 +246,33 @@ sorf_energy_grad_kernel(const float *__restrict__ x, const int *__restrict__ gro
     const int T = TT > 0 ? TT : T_rt;  // compile-time trip count for the common single-transform model
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane / C::L, l = lane % C::L;  // vector within the warp, lane within the vector
-    float *slab = smem + warp * C::WARP_FLOATS + g * C::SLAB;
+    float *slab = smem + warp * (ATOMS * C::WARP_FLOATS) + g * C::SLAB;
 
-    const long row = (long)blockIdx.x * WARPS + warp;
-    if (row >= group_start[nel]) return;
-    if (slot_of_row[row] < 0) {  // padding row of an element group
-        if (lane == 0) atom_energy[row] = 0.f;
+    // A warp handles ATOMS consecutive rows (same element: groups are padded to a multiple of WARPS * ATOMS rows) and
+    // shares every parameter load between them.
+    const long row0 = ((long)blockIdx.x * WARPS + warp) * ATOMS;
+    if (row0 >= group_start[nel]) return;
+    int el = 0;
+    while (el + 1 < nel && row0 >= group_start[el + 1]) ++el;
+
+    float xr[ATOMS][16], gx[ATOMS][16], eacc[ATOMS];
+    bool live[ATOMS];
+#pragma unroll
+    for (int a = 0; a < ATOMS; ++a) {
+        live[a] = slot_of_row[row0 + a] >= 0;  // padding rows of an element group are computed on zeros and not stored
+        if (live[a]) load16_row(xr[a], x + (size_t)(row0 + a) * N + l * 16);
+        else {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) xr[a][e] = 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < 16; ++e) gx[a][e] = 0.f;
+        eacc[a] = 0.f;
+    }
+    if (ATOMS == 1 && !live[0]) {
+        if (lane == 0) atom_energy[row0] = 0.f;
         return;
     }
-    int el = 0;
-    while (el + 1 < nel && row >= group_start[el + 1]) ++el;
-
-    float xr[16], gx[16];
-    load16_row(xr, x + (size_t)row * N + l * 16);
-#pragma unroll
-    for (int e = 0; e < 16; ++e) gx[e] = 0.f;
-    float eacc = 0.f;
 
     const size_t pos = (size_t)l * 4;  // interleaved parameter blocks: float4 index q*L + l
     const float *Dp_e = Dp + (size_t)el * S * T * N;
@@ -200,23 +282,29 @@ sorf_energy_grad_kernel(const float *__restrict__ x, const int *__restrict__ gro
     for (int s0 = 0; s0 < S; s0 += C::V) {
         const int sc = s0 + g;
         const float *Ds = Dp_e + (size_t)sc * T * N + pos;
-        float u[16], c[16];
+        float u[ATOMS][16], c[16];
         bool in_a = true;
         if (TT == 1) {
             // single transform: the sign diagonal stays in registers for the way back
             load16<C::L>(c, Ds);
 #pragma unroll
-            for (int e = 0; e < 16; ++e) u[e] = xr[e] * c[e];
-            fwht_flip<LOG2N>(u, slab, l, lane, true);
+            for (int a = 0; a < ATOMS; ++a)
+#pragma unroll
+                for (int e = 0; e < 16; ++e) u[a][e] = xr[a][e] * c[e];
+            fwht_flip_n<LOG2N, ATOMS>(u, slab, l, lane, true);
             in_a = false;
         } else {
 #pragma unroll
-            for (int e = 0; e < 16; ++e) u[e] = xr[e];
+            for (int a = 0; a < ATOMS; ++a)
+#pragma unroll
+                for (int e = 0; e < 16; ++e) u[a][e] = xr[a][e];
             for (int m = 0; m < T; ++m) {
                 load16<C::L>(c, Ds + (size_t)m * N);
 #pragma unroll
-                for (int e = 0; e < 16; ++e) u[e] *= c[e];
-                fwht_flip<LOG2N>(u, slab, l, lane, in_a);
+                for (int a = 0; a < ATOMS; ++a)
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) u[a][e] *= c[e];
+                fwht_flip_n<LOG2N, ATOMS>(u, slab, l, lane, in_a);
                 in_a = !in_a;
             }
         }
@@ -228,32 +316,40 @@ sorf_energy_grad_kernel(const float *__restrict__ x, const int *__restrict__ gro
                 const float4 b4 = __ldg(bq + q * C::L), a4 = __ldg(aq + q * C::L);
                 const float bb[4] = {b4.x, b4.y, b4.z, b4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w};
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const int e = 4 * q + r;
-                    const float arg = fmaf(u[e], scale, bb[r]);
-                    float sn, cs;
-                    if (FAST) __sincosf(arg, &sn, &cs);
-                    else sincosf(arg, &sn, &cs);
-                    eacc = fmaf(aa[r], cs, eacc);
-                    u[e] = -aa[r] * sn;
-                }
+                for (int a = 0; a < ATOMS; ++a)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const int e = 4 * q + r;
+                        const float arg = fmaf(u[a][e], scale, bb[r]);
+                        float sn, cs;
+                        if (FAST) __sincosf(arg, &sn, &cs);
+                        else sincosf(arg, &sn, &cs);
+                        eacc[a] = fmaf(aa[r], cs, eacc[a]);
+                        u[a][e] = -aa[r] * sn;
+                    }
             }
         }
         if (TT == 1) {
-            fwht_flip<LOG2N>(u, slab, l, lane, false);
+            fwht_flip_n<LOG2N, ATOMS>(u, slab, l, lane, false);
 #pragma unroll
-            for (int e = 0; e < 16; ++e) gx[e] = fmaf(u[e], c[e], gx[e]);
+            for (int a = 0; a < ATOMS; ++a)
+#pragma unroll
+                for (int e = 0; e < 16; ++e) gx[a][e] = fmaf(u[a][e], c[e], gx[a][e]);
         } else {
             for (int m = T - 1; m >= 0; --m) {
-                fwht_flip<LOG2N>(u, slab, l, lane, in_a);
+                fwht_flip_n<LOG2N, ATOMS>(u, slab, l, lane, in_a);
                 in_a = !in_a;
                 load16<C::L>(c, Ds + (size_t)m * N);
                 if (m > 0) {
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) u[e] *= c[e];
+                    for (int a = 0; a < ATOMS; ++a)
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) u[a][e] *= c[e];
                 } else {
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) gx[e] = fmaf(u[e], c[e], gx[e]);
+                    for (int a = 0; a < ATOMS; ++a)
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) gx[a][e] = fmaf(u[a][e], c[e], gx[a][e]);
                 }
             }
         }
@@ -261,17 +357,21 @@ sorf_energy_grad_kernel(const float *__restrict__ x, const int *__restrict__ gro
 
     // sum the V stacks processed side by side, then one store per atom
 #pragma unroll
-    for (int off = C::L; off < 32; off <<= 1)
+    for (int a = 0; a < ATOMS; ++a) {
 #pragma unroll
-        for (int e = 0; e < 16; ++e) gx[e] += __shfl_xor_sync(QMLB_FULL_MASK, gx[e], off);
-    eacc = warp_sum(eacc);
-    if (g == 0) {
-        float4 *dst = reinterpret_cast<float4 *>(grad_x + (size_t)row * N + l * 16);
+        for (int off = C::L; off < 32; off <<= 1)
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-            dst[q] = make_float4(gx[4 * q] * scale, gx[4 * q + 1] * scale, gx[4 * q + 2] * scale, gx[4 * q + 3] * scale);
+            for (int e = 0; e < 16; ++e) gx[a][e] += __shfl_xor_sync(QMLB_FULL_MASK, gx[a][e], off);
+        const float esum = warp_sum(eacc[a]);
+        if (g == 0 && live[a]) {
+            float4 *dst = reinterpret_cast<float4 *>(grad_x + (size_t)(row0 + a) * N + l * 16);
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                dst[q] = make_float4(gx[a][4 * q] * scale, gx[a][4 * q + 1] * scale, gx[a][4 * q + 2] * scale,
+                                     gx[a][4 * q + 3] * scale);
+        }
+        if (lane == 0) atom_energy[row0 + a] = live[a] ? esum : 0.f;
     }
-    if (lane == 0) atom_energy[row] = eacc;
 }
 
 // Source element of packed float index p (0..N-1) of one block: p = (q*L + l)*4 + r holds register e = 4q + r of
@@ -325,20 +425,28 @@ int ilog2_exact(int n) {
     return (1 << l) == n ? l : -1;
 }
 
+#ifndef SORF_ATOMS
+#define SORF_ATOMS 2
+#endif
+
 template <int LOG2N>
 int launch_fused(const float *x, const int *group_start, const int *slot_of_row, int nel, size_t rows_cap, int S, int T,
                  float scale, const float *Dp, const float *bp, const float *ap, int fast, float *atom_energy,
                  float *grad_x, cudaStream_t st) {
     using C = Cfg<LOG2N>;
-    const size_t smem = sizeof(float) * WARPS * C::WARP_FLOATS;
-    const unsigned grid = (unsigned)((rows_cap + WARPS - 1) / WARPS);
-#define QMLB_LAUNCH(FASTV, TTV)                                                                                      \
-    sorf_energy_grad_kernel<LOG2N, FASTV, TTV><<<grid, WARPS * 32, smem, st>>>(x, group_start, slot_of_row, nel, S, T, \
-                                                                               scale, Dp, bp, ap, atom_energy, grad_x)
+    // two atoms per warp share the parameter loads when the model has a single transform and 16 <= N... (the common case)
+    constexpr int ATOMS_FAST = (LOG2N >= 6 && LOG2N <= 8) ? SORF_ATOMS : 1;
+#define QMLB_LAUNCH(FASTV, TTV, AT)                                                                                    \
+    do {                                                                                                              \
+        const size_t smem = sizeof(float) * WARPS * AT * C::WARP_FLOATS;                                              \
+        const unsigned grid = (unsigned)((rows_cap + WARPS * AT - 1) / (WARPS * AT));                                 \
+        sorf_energy_grad_kernel<LOG2N, FASTV, TTV, AT><<<grid, WARPS * 32, smem, st>>>(                               \
+            x, group_start, slot_of_row, nel, S, T, scale, Dp, bp, ap, atom_energy, grad_x);                           \
+    } while (0)
     if (T == 1) {
-        if (fast) QMLB_LAUNCH(true, 1); else QMLB_LAUNCH(false, 1);
+        if (fast) QMLB_LAUNCH(true, 1, ATOMS_FAST); else QMLB_LAUNCH(false, 1, 1);
     } else {
-        if (fast) QMLB_LAUNCH(true, 0); else QMLB_LAUNCH(false, 0);
+        if (fast) QMLB_LAUNCH(true, 0, 1); else QMLB_LAUNCH(false, 0, 1);
     }
 #undef QMLB_LAUNCH
     return qmlb::check_launch("qmlb_sorf_energy_grad");
