@@ -16,7 +16,10 @@
 
 namespace {
 
-constexpr int FCHL_WARPS = 8;
+#ifndef QMLB_FCHL_WARPS
+#define QMLB_FCHL_WARPS 4
+#endif
+constexpr int FCHL_WARPS = QMLB_FCHL_WARPS;
 constexpr int FCHL_THREADS = FCHL_WARPS * 32;
 constexpr float ZETA2 = 0.014383766711652736f;  // 2 * exp(-pi^2 / 2)
 
