@@ -306,12 +306,14 @@ def sorf_predict(X, Z, atom_counts, fchl, elements, reductors, packed, S, T, sig
     nel, repsize, N = reductors.shape
     lib = _lib.load()
     upper = nb * A if n_atoms_upper is None else int(n_atoms_upper)
-    need = lib.qmlb_predict_workspace_bytes(nb, A, upper, nel, repsize, N)
-    ws = _workspace(X.device, need)
     if energy is None:
         energy = torch.empty(nb, dtype=torch.float32, device=X.device)
     if grad_X is None:
         grad_X = torch.empty(nb, A, 3, dtype=torch.float32, device=X.device)
+    if nb == 0:
+        return energy, grad_X
+    need = lib.qmlb_predict_workspace_bytes(nb, A, upper, nel, repsize, N)
+    ws = _workspace(X.device, need)
     pc = fchl.c()
     check(lib.qmlb_sorf_predict(_p(X, torch.float32, 'coordinates'), _p(Z, torch.float32, 'charges'),
                                 _p(atom_counts, torch.int32, 'atom_counts'), nb, A, ctypes.byref(pc), _p(cell), _p(inv_cell),
@@ -345,11 +347,13 @@ def rff_predict(X, Z, atom_counts, fchl, elements, reductors, W, b, alpha, cell=
     D = W.shape[-1]
     lib = _lib.load()
     upper = nb * A if n_atoms_upper is None else int(n_atoms_upper)
-    ws = _workspace(X.device, lib.qmlb_predict_workspace_bytes(nb, A, upper, nel, repsize, N))
     if energy is None:
         energy = torch.empty(nb, dtype=torch.float32, device=X.device)
     if grad_X is None:
         grad_X = torch.empty(nb, A, 3, dtype=torch.float32, device=X.device)
+    if nb == 0:
+        return energy, grad_X
+    ws = _workspace(X.device, lib.qmlb_predict_workspace_bytes(nb, A, upper, nel, repsize, N))
     pc = fchl.c()
     check(lib.qmlb_rff_predict(_p(X, torch.float32, 'coordinates'), _p(Z, torch.float32, 'charges'),
                                _p(atom_counts, torch.int32, 'atom_counts'), nb, A, ctypes.byref(pc), _p(cell), _p(inv_cell),

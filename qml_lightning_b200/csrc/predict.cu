@@ -43,9 +43,9 @@ int predict_pipeline(const float *X, const float *Z, const int *atom_counts, int
                      const float *cell, const float *inv_cell, const float *elements, int nelements,
                      const float *reductors, int npcas, size_t n_atoms_upper, void *workspace, size_t workspace_bytes,
                      float *energy, float *grad_X, qmlb_stream_t stream, const char *who, FeatureStage features) {
-    QMLB_REQUIRE(X && Z && atom_counts && p && elements && reductors && workspace && energy && grad_X, "%s: null argument", who);
     QMLB_REQUIRE(nb >= 0 && A > 0 && nelements > 0 && npcas > 0, "%s: bad sizes", who);
-    if (nb == 0) return QMLB_OK;
+    if (nb == 0) return QMLB_OK;  // empty batch: nothing to launch (its tensors have no storage to point at)
+    QMLB_REQUIRE(X && Z && atom_counts && p && elements && reductors && workspace && energy && grad_X, "%s: null argument", who);
     const int repsize = qmlb_fchl19_repsize(p->nspecies, p->nRs2, p->nRs3);
     const Workspace W(nb, A, n_atoms_upper, nelements, repsize, npcas);
     QMLB_REQUIRE(workspace_bytes >= W.total, "%s: workspace of %zu bytes given, %zu needed", who, workspace_bytes, W.total);
@@ -79,7 +79,7 @@ extern "C" int qmlb_sorf_predict(const float *X, const float *Z, const int *atom
                                  const void *packed, int S, int T, float sigma, int fast_math, size_t n_atoms_upper,
                                  void *workspace, size_t workspace_bytes, float *energy, float *grad_X,
                                  qmlb_stream_t stream) {
-    QMLB_REQUIRE(packed, "qmlb_sorf_predict: null argument");
+    QMLB_REQUIRE(packed || nb == 0, "qmlb_sorf_predict: null argument");
     return predict_pipeline(X, Z, atom_counts, nb, A, p, cell, inv_cell, elements, nelements, reductors, npcas,
                             n_atoms_upper, workspace, workspace_bytes, energy, grad_X, stream, "qmlb_sorf_predict",
                             [&](const float *x, const int *group_start, const int *slot_of_row, size_t rows_cap,
@@ -95,7 +95,7 @@ extern "C" int qmlb_rff_predict(const float *X, const float *Z, const int *atom_
                                 const float *b, const float *alpha, int nfeatures, int fast_math, size_t n_atoms_upper,
                                 void *workspace, size_t workspace_bytes, float *energy, float *grad_X,
                                 qmlb_stream_t stream) {
-    QMLB_REQUIRE(W && b && alpha, "qmlb_rff_predict: null argument");
+    QMLB_REQUIRE((W && b && alpha) || nb == 0, "qmlb_rff_predict: null argument");
     return predict_pipeline(X, Z, atom_counts, nb, A, p, cell, inv_cell, elements, nelements, reductors, npcas,
                             n_atoms_upper, workspace, workspace_bytes, energy, grad_X, stream, "qmlb_rff_predict",
                             [&](const float *x, const int *group_start, const int *slot_of_row, size_t rows_cap,

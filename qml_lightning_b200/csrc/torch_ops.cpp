@@ -316,6 +316,7 @@ class SorfEnergyFn : public torch::autograd::Function<SorfEnergyFn> {
         char *wp = reinterpret_cast<char *>(((uintptr_t)ws.data_ptr<uint8_t>() + 255) & ~(uintptr_t)255);
         Tensor E = torch::empty({b.nb}, b.X.options());
         Tensor gX = torch::empty({b.nb, b.A, 3}, b.X.options());
+        if (b.nb > 0)
         check(qmlb_sorf_predict(b.X.data_ptr<float>(), b.Z.data_ptr<float>(), b.counts.data_ptr<int>(), b.nb, b.A, &f.p,
                                 cell_ptr(b.cell), cell_ptr(b.inv_cell), el.data_ptr<float>(), nel, red.data_ptr<float>(),
                                 npcas, pk.data_ptr<float>(), (int)nstacks, (int)ntransforms, (float)sigma, fast_math ? 1 : 0,
@@ -365,6 +366,7 @@ class RffEnergyFn : public torch::autograd::Function<RffEnergyFn> {
         char *wp = reinterpret_cast<char *>(((uintptr_t)ws.data_ptr<uint8_t>() + 255) & ~(uintptr_t)255);
         Tensor E = torch::empty({bt.nb}, bt.X.options());
         Tensor gX = torch::empty({bt.nb, bt.A, 3}, bt.X.options());
+        if (bt.nb > 0)
         check(qmlb_rff_predict(bt.X.data_ptr<float>(), bt.Z.data_ptr<float>(), bt.counts.data_ptr<int>(), bt.nb, bt.A, &f.p,
                                cell_ptr(bt.cell), cell_ptr(bt.inv_cell), el.data_ptr<float>(), nel, red.data_ptr<float>(), npcas,
                                Wc.data_ptr<float>(), bc.data_ptr<float>(), ac.data_ptr<float>(), D, fast_math ? 1 : 0, upper, wp,
