@@ -233,6 +233,20 @@ int qmlb_rff_energy_grad(const float *x, const int *group_start, const int *slot
                          int npcas, int nfeatures, const float *W, const float *b, const float *alpha, int fast_math,
                          float *atom_energy, float *grad_x, qmlb_stream_t stream);
 
+/* Tensor-core version of qmlb_rff_energy_grad (same upstream lines; tcgen05.mma on fp16 hi/lo operand pairs with fp32
+ * accumulation, results within fp32 rounding of the FFMA version).  The model parameters are re-packed once:
+ *   qmlb_rff_pack_bytes -> allocate (256-byte aligned) -> qmlb_rff_pack(W, b, alpha) -> qmlb_rff_energy_grad_tc per batch.
+ * qmlb_rff_pack must be called again whenever W, b or alpha change.  Feature counts are padded to a multiple of 32
+ * inside the packed buffer (padding features carry zero weight).  qmlb_rff_pack_bytes returns 0 for unsupported
+ * sizes.  Operands larger than 2^41 in magnitude are outside the supported range.  A kernel that is handed parameters
+ * packed for another npcas or element count does nothing and reports through qmlb_tc_timeouts(). */
+size_t qmlb_rff_pack_bytes(int nelements, int npcas, int nfeatures);
+int qmlb_rff_pack(const float *W, const float *b, const float *alpha, int nelements, int npcas, int nfeatures, void *packed,
+                  size_t packed_bytes, qmlb_stream_t stream);
+int qmlb_rff_energy_grad_tc(const float *x, const int *group_start, const int *slot_of_row, int nelements, size_t rows_cap,
+                            int npcas, const void *packed, int fast_math, float *atom_energy, float *grad_x,
+                            qmlb_stream_t stream);
+
 /* RandomFourrierFeaturesModel.forward + autograd.grad (models/random_features.py:69-102, 104-158) as one call;
  * same conventions and workspace as qmlb_sorf_predict. */
 int qmlb_rff_predict(const float *X, const float *Z, const int *atom_counts, int nb, int A, const qmlb_fchl_params *p,
@@ -240,6 +254,13 @@ int qmlb_rff_predict(const float *X, const float *Z, const int *atom_counts, int
                      const float *reductors, int npcas, const float *W, const float *b, const float *alpha, int nfeatures,
                      int fast_math, size_t n_atoms_upper, void *workspace, size_t workspace_bytes, float *energy,
                      float *grad_X, qmlb_stream_t stream);
+
+/* qmlb_rff_predict on parameters packed by qmlb_rff_pack: the feature stage runs on the tensor cores
+ * (qmlb_rff_energy_grad_tc).  This is the path RandomFourrierFeaturesModel uses. */
+int qmlb_rff_predict_packed(const float *X, const float *Z, const int *atom_counts, int nb, int A, const qmlb_fchl_params *p,
+                            const float *cell, const float *inv_cell, const float *elements, int nelements,
+                            const float *reductors, int npcas, const void *packed, int fast_math, size_t n_atoms_upper,
+                            void *workspace, size_t workspace_bytes, float *energy, float *grad_X, qmlb_stream_t stream);
 
 /* Projection of an element-grouped explicit Jacobian: project_derivative = einsum('jmnk,kl->jmnl')
  * (representations/dimensionality_reduction.py:61-72; call site models/kernel.py:160).

@@ -52,9 +52,15 @@ SIGNATURES = {
                                   c_void_p, c_void_p]),
     'qmlb_rff_energy_grad': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                      c_int, c_void_p, c_void_p, c_void_p]),
+    'qmlb_rff_pack_bytes': (c_size_t, [c_int, c_int, c_int]),
+    'qmlb_rff_pack': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    'qmlb_rff_energy_grad_tc': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                        c_void_p]),
     'qmlb_rff_predict': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, P, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                  c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_size_t, c_void_p, c_size_t, c_void_p,
                                  c_void_p, c_void_p]),
+    'qmlb_rff_predict_packed': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, P, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                        c_int, c_void_p, c_int, c_size_t, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]),
     'qmlb_pca_project_jacobian': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_int, c_int, c_int, c_void_p, c_void_p]),
     'qmlb_sorf_train_features': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                          c_int, c_int, c_size_t, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p,

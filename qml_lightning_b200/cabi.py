@@ -338,6 +338,32 @@ def rff_energy_grad(x, grouping, W, b, alpha, fast_math=True):
     return atom_energy, grad_x
 
 
+def rff_pack(W, b, alpha):
+    """Packed fp16 hi/lo image of the RFF parameters for the tensor-core kernel (``qmlb_rff_pack``); uint8 tensor."""
+    nel, K, D = W.shape
+    lib = _lib.load()
+    nbytes = lib.qmlb_rff_pack_bytes(nel, K, D)
+    if nbytes == 0:
+        raise RuntimeError(f'qmlb_rff_pack: unsupported sizes (nelements={nel}, npcas={K}, nfeatures={D})')
+    packed = torch.empty(nbytes, dtype=torch.uint8, device=W.device)
+    check(lib.qmlb_rff_pack(_p(W.contiguous(), torch.float32, 'W'), _p(b.contiguous(), torch.float32, 'b'),
+                            _p(alpha.contiguous(), torch.float32, 'alpha'), nel, K, D, _p(packed), nbytes, _stream(W.device)),
+          'qmlb_rff_pack')
+    return packed
+
+
+def rff_energy_grad_tc(x, grouping, packed, nelements, fast_math=True):
+    """Tensor-core version of :func:`rff_energy_grad` on parameters packed by :func:`rff_pack`."""
+    rows = grouping.rows_cap
+    K = x.shape[1]
+    atom_energy = torch.empty(rows, dtype=torch.float32, device=x.device)
+    grad_x = torch.empty(rows, K, dtype=torch.float32, device=x.device)
+    check(_lib.load().qmlb_rff_energy_grad_tc(_p(x, torch.float32, 'x'), _p(grouping.group_start), _p(grouping.slot_of_row),
+                                              int(nelements), rows, K, _p(packed), int(bool(fast_math)), _p(atom_energy),
+                                              _p(grad_x), _stream(x.device)), 'qmlb_rff_energy_grad_tc')
+    return atom_energy, grad_x
+
+
 def rff_predict(X, Z, atom_counts, fchl, elements, reductors, W, b, alpha, cell=None, inv_cell=None, n_atoms_upper=None,
                 fast_math=True, energy=None, grad_X=None):
     """Energies ``[nb]`` and ``dE/dX [nb,A,3]`` of the RFF model through ``qmlb_rff_predict``."""
@@ -362,6 +388,31 @@ def rff_predict(X, Z, atom_counts, fchl, elements, reductors, W, b, alpha, cell=
                                _p(W.contiguous(), torch.float32, 'W'), _p(b.contiguous(), torch.float32, 'b'),
                                _p(alpha.contiguous(), torch.float32, 'alpha'), D, int(bool(fast_math)), upper, _p(ws),
                                ws.numel(), _p(energy), _p(grad_X), _stream(X.device)), 'qmlb_rff_predict')
+    return energy, grad_X
+
+
+def rff_predict_packed(X, Z, atom_counts, fchl, elements, reductors, packed, cell=None, inv_cell=None, n_atoms_upper=None,
+                       fast_math=True, energy=None, grad_X=None):
+    """:func:`rff_predict` on parameters packed by :func:`rff_pack` (tensor-core feature stage, ``qmlb_rff_predict_packed``)."""
+    X, Z, atom_counts, nb, A = _batch(X, Z, atom_counts)
+    cell, inv_cell = _cells(cell, inv_cell)
+    nel, repsize, N = reductors.shape
+    lib = _lib.load()
+    upper = nb * A if n_atoms_upper is None else int(n_atoms_upper)
+    if energy is None:
+        energy = torch.empty(nb, dtype=torch.float32, device=X.device)
+    if grad_X is None:
+        grad_X = torch.empty(nb, A, 3, dtype=torch.float32, device=X.device)
+    if nb == 0:
+        return energy, grad_X
+    ws = _workspace(X.device, lib.qmlb_predict_workspace_bytes(nb, A, upper, nel, repsize, N))
+    pc = fchl.c()
+    check(lib.qmlb_rff_predict_packed(_p(X, torch.float32, 'coordinates'), _p(Z, torch.float32, 'charges'),
+                                      _p(atom_counts, torch.int32, 'atom_counts'), nb, A, ctypes.byref(pc), _p(cell),
+                                      _p(inv_cell), _p(elements.contiguous(), torch.float32, 'elements'), nel,
+                                      _p(reductors.contiguous(), torch.float32, 'reductors'), N, _p(packed),
+                                      int(bool(fast_math)), upper, _p(ws), ws.numel(), _p(energy), _p(grad_X),
+                                      _stream(X.device)), 'qmlb_rff_predict_packed')
     return energy, grad_X
 
 

@@ -104,3 +104,18 @@ extern "C" int qmlb_rff_predict(const float *X, const float *Z, const int *atom_
                                                             nfeatures, W, b, alpha, fast_math, atom_energy, gx, stream);
                             });
 }
+
+extern "C" int qmlb_rff_predict_packed(const float *X, const float *Z, const int *atom_counts, int nb, int A,
+                                       const qmlb_fchl_params *p, const float *cell, const float *inv_cell,
+                                       const float *elements, int nelements, const float *reductors, int npcas,
+                                       const void *packed, int fast_math, size_t n_atoms_upper, void *workspace,
+                                       size_t workspace_bytes, float *energy, float *grad_X, qmlb_stream_t stream) {
+    QMLB_REQUIRE(packed || nb == 0, "qmlb_rff_predict_packed: null argument");
+    return predict_pipeline(X, Z, atom_counts, nb, A, p, cell, inv_cell, elements, nelements, reductors, npcas,
+                            n_atoms_upper, workspace, workspace_bytes, energy, grad_X, stream, "qmlb_rff_predict_packed",
+                            [&](const float *x, const int *group_start, const int *slot_of_row, size_t rows_cap,
+                                float *atom_energy, float *gx) {
+                                return qmlb_rff_energy_grad_tc(x, group_start, slot_of_row, nelements, rows_cap, npcas, packed,
+                                                               fast_math, atom_energy, gx, stream);
+                            });
+}

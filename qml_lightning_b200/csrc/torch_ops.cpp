@@ -341,25 +341,41 @@ Tensor sorf_energy(const Tensor &X, const Tensor &Z, const Tensor &atom_counts, 
                                packed, nstacks, ntransforms, sigma, n_atoms_upper, fast_math)[0];
 }
 
+// RFF twin of sorf_pack: fp16 hi/lo chunk images of W plus bias and weights for the tensor-core feature kernel.
+Tensor rff_pack(const Tensor &W, const Tensor &b, const Tensor &alpha) {
+    TORCH_CHECK(W.device().type() == torch::kCUDA, "W must be a CUDA tensor");
+    c10::cuda::CUDAGuard guard(W.device());
+    Tensor Wc = f32c(W), bc = f32c(b.to(Wc.device())), ac = f32c(alpha.to(Wc.device()));
+    TORCH_CHECK(Wc.dim() == 3, "W must be [nelements, npcas, D]");
+    const int nel = (int)Wc.size(0), K = (int)Wc.size(1), D = (int)Wc.size(2);
+    TORCH_CHECK(bc.numel() == (int64_t)nel * D && ac.numel() == D, "b must be [nelements, D] and alpha [D]");
+    const size_t bytes = qmlb_rff_pack_bytes(nel, K, D);
+    TORCH_CHECK(bytes > 0, "rff_pack: npcas must be 32, 64, 128 or 256");
+    Tensor packed = torch::empty({(int64_t)bytes}, Wc.options().dtype(torch::kUInt8));
+    check(qmlb_rff_pack(Wc.data_ptr<float>(), bc.data_ptr<float>(), ac.data_ptr<float>(), nel, K, D, packed.data_ptr<uint8_t>(),
+                        bytes, current_stream()),
+          "rff_pack");
+    return packed;
+}
+
 // RFF twin of SorfEnergyFn.
 class RffEnergyFn : public torch::autograd::Function<RffEnergyFn> {
    public:
     static variable_list forward(AutogradContext *ctx, Tensor X, Tensor Z, Tensor atom_counts, Tensor cell, Tensor inv_cell,
                                  Tensor species, Tensor Rs2, Tensor Rs3, Tensor fchl_scalars, Tensor elements,
-                                 Tensor reductors, Tensor W, Tensor b, Tensor alpha, int64_t n_atoms_upper, bool fast_math) {
+                                 Tensor reductors, Tensor packed, int64_t n_atoms_upper, bool fast_math) {
         Batch bt(X, Z, atom_counts, cell, inv_cell);
         c10::cuda::CUDAGuard guard(bt.X.device());
         Tensor sc = fchl_scalars.to(torch::kCPU).to(torch::kFloat64).contiguous();
         TORCH_CHECK(sc.numel() == 6, "fchl_scalars must hold eta2, eta3, two_body_decay, three_body_weight, three_body_decay, rcut");
         const double *s = sc.data_ptr<double>();
         Fchl f(species, Rs2, Rs3, s[0], s[1], s[2], s[3], s[4], s[5], bt.X.device());
-        Tensor el = f32c(elements.to(bt.X.device())), red = f32c(reductors), Wc = f32c(W), bc = f32c(b),
-               ac = f32c(alpha.to(bt.X.device()));
+        Tensor el = f32c(elements.to(bt.X.device())), red = f32c(reductors);
         TORCH_CHECK(red.dim() == 3 && red.size(0) == el.numel() && red.size(1) == f.repsize(),
                     "reductors must be [nelements, repsize, npcas]");
-        TORCH_CHECK(Wc.dim() == 3 && Wc.size(0) == el.numel() && Wc.size(1) == red.size(2) && bc.numel() == el.numel() * Wc.size(2) &&
-                        ac.numel() == Wc.size(2), "W must be [nelements, npcas, D], b [nelements, D], alpha [D]");
-        const int nel = (int)el.numel(), npcas = (int)red.size(2), D = (int)Wc.size(2);
+        TORCH_CHECK(packed.device() == bt.X.device() && packed.scalar_type() == torch::kUInt8 && packed.is_contiguous(),
+                    "packed must be the uint8 tensor returned by rff_pack, on the device of X");
+        const int nel = (int)el.numel(), npcas = (int)red.size(2);
         const size_t upper = n_atoms_upper > 0 ? (size_t)n_atoms_upper : (size_t)bt.nb * bt.A;
         const size_t bytes = qmlb_predict_workspace_bytes(bt.nb, bt.A, upper, nel, f.repsize(), npcas);
         Tensor ws = torch::empty({(int64_t)bytes + 256}, bt.X.options().dtype(torch::kUInt8));
@@ -367,10 +383,10 @@ class RffEnergyFn : public torch::autograd::Function<RffEnergyFn> {
         Tensor E = torch::empty({bt.nb}, bt.X.options());
         Tensor gX = torch::empty({bt.nb, bt.A, 3}, bt.X.options());
         if (bt.nb > 0)
-        check(qmlb_rff_predict(bt.X.data_ptr<float>(), bt.Z.data_ptr<float>(), bt.counts.data_ptr<int>(), bt.nb, bt.A, &f.p,
-                               cell_ptr(bt.cell), cell_ptr(bt.inv_cell), el.data_ptr<float>(), nel, red.data_ptr<float>(), npcas,
-                               Wc.data_ptr<float>(), bc.data_ptr<float>(), ac.data_ptr<float>(), D, fast_math ? 1 : 0, upper, wp,
-                               bytes, E.data_ptr<float>(), gX.data_ptr<float>(), current_stream()),
+        check(qmlb_rff_predict_packed(bt.X.data_ptr<float>(), bt.Z.data_ptr<float>(), bt.counts.data_ptr<int>(), bt.nb, bt.A,
+                                      &f.p, cell_ptr(bt.cell), cell_ptr(bt.inv_cell), el.data_ptr<float>(), nel,
+                                      red.data_ptr<float>(), npcas, packed.data_ptr<uint8_t>(), fast_math ? 1 : 0, upper, wp,
+                                      bytes, E.data_ptr<float>(), gX.data_ptr<float>(), current_stream()),
               "rff_energy");
         ctx->save_for_backward({gX});
         return {E};
@@ -379,16 +395,16 @@ class RffEnergyFn : public torch::autograd::Function<RffEnergyFn> {
         Tensor gX = ctx->get_saved_variables()[0];
         Tensor g = grad_output[0].to(gX.dtype()).reshape({-1, 1, 1}) * gX;
         Tensor u;
-        return {g, u, u, u, u, u, u, u, u, u, u, u, u, u, u, u};
+        return {g, u, u, u, u, u, u, u, u, u, u, u, u, u};
     }
 };
 
 Tensor rff_energy(const Tensor &X, const Tensor &Z, const Tensor &atom_counts, const Tensor &cell, const Tensor &inv_cell,
                   const Tensor &species, const Tensor &Rs2, const Tensor &Rs3, const Tensor &fchl_scalars,
-                  const Tensor &elements, const Tensor &reductors, const Tensor &W, const Tensor &b, const Tensor &alpha,
-                  int64_t n_atoms_upper, bool fast_math) {
-    return RffEnergyFn::apply(X, Z, atom_counts, cell, inv_cell, species, Rs2, Rs3, fchl_scalars, elements, reductors, W, b,
-                              alpha, n_atoms_upper, fast_math)[0];
+                  const Tensor &elements, const Tensor &reductors, const Tensor &packed, int64_t n_atoms_upper,
+                  bool fast_math) {
+    return RffEnergyFn::apply(X, Z, atom_counts, cell, inv_cell, species, Rs2, Rs3, fchl_scalars, elements, reductors, packed,
+                              n_atoms_upper, fast_math)[0];
 }
 
 }  // namespace
@@ -409,5 +425,6 @@ TORCH_LIBRARY(qml_lightning_sorf, m) {
 TORCH_LIBRARY(qml_lightning_b200, m) {
     m.def("sorf_pack", sorf_pack);
     m.def("sorf_energy", sorf_energy);
+    m.def("rff_pack", rff_pack);
     m.def("rff_energy", rff_energy);
 }

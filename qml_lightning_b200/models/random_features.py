@@ -22,6 +22,8 @@ class RandomFourrierFeaturesModel(BaseKernel, torch.nn.Module):
         self.alpha = torch.zeros(self._nfeatures, device=self.device, dtype=torch.float)
         self.is_trained = False
         self.fast_math = bool(fast_math)
+        self.packed = torch.zeros(1, dtype=torch.uint8, device=self.device)
+        self._parameters_changed()
 
     def sample_elemental_basis(self):
         """W ~ N(0,1)/(2 sigma^2), b ~ U(0, 2 pi) per element (upstream :42-55)."""
@@ -39,6 +41,7 @@ class RandomFourrierFeaturesModel(BaseKernel, torch.nn.Module):
     def set_alpha(self, alpha):
         self.alpha = alpha.to(self.device)
         self.is_trained = True
+        self._parameters_changed()
 
     # ---- training ------------------------------------------------------------------------------------------------
     def training_rows(self, data, with_forces):
@@ -60,7 +63,9 @@ class RandomFourrierFeaturesModel(BaseKernel, torch.nn.Module):
         return cabi.rff_train_features(x, dx, self.W, self.b, g, counts, nb, A)
 
     def _parameters_changed(self):
-        pass
+        """Rebuild the packed image of (W, b, alpha) that the tensor-core feature kernel reads; call after changing any
+        of them by hand."""
+        self.packed = torch.ops.qml_lightning_b200.rff_pack(self.W, self.b, self.alpha.float())
 
     # ---- inference -----------------------------------------------------------------------------------------------
     def forward(self, X, Z, atomIDs, molIDs, atom_counts, cell=torch.empty(0, 3, 3), inv_cell=torch.empty(0, 3, 3)):
@@ -70,16 +75,16 @@ class RandomFourrierFeaturesModel(BaseKernel, torch.nn.Module):
         assert atom_counts.device == X.device, "atom_counts tensor must reside on the same GPU as X"
         return torch.ops.qml_lightning_b200.rff_energy(X, Z, atom_counts, cell, inv_cell, self.rep.species, self.rep.Rs2,
                                                        self.rep.Rs3, self.rep.kernel_scalars, self.species, self.reductors,
-                                                       self.W, self.b, self.alpha, atomIDs.shape[0], self.fast_math)
+                                                       self.packed, atomIDs.shape[0], self.fast_math)
 
     def predict_opt(self, coordinates, charges, atomIDs, molIDs, natom_counts, zcells=None, zinv_cells=None, forces=True,
                     print_info=False, profiler=False):
         if self.is_trained is False:
             raise RuntimeError("must train the model first by calling train()!")
         dev = coordinates.device
-        energies, grad = cabi.rff_predict(coordinates, charges, natom_counts, self.rep.kernel_params(dev), self.species,
-                                          self.reductors, self.W, self.b, self.alpha.float(), zcells, zinv_cells,
-                                          n_atoms_upper=atomIDs.shape[0], fast_math=self.fast_math)
+        energies, grad = cabi.rff_predict_packed(coordinates, charges, natom_counts, self.rep.kernel_params(dev), self.species,
+                                                 self.reductors, self.packed, zcells, zinv_cells,
+                                                 n_atoms_upper=atomIDs.shape[0], fast_math=self.fast_math)
         if print_info:
             torch.cuda.synchronize()
             print("prediction for", coordinates.shape[0], "molecules")

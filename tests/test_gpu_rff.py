@@ -18,10 +18,14 @@ DEV = 'cuda:0'
 
 @pytest.mark.parametrize('K', [32, 64, 128, 256])
 @pytest.mark.parametrize('fast', [False, True])
-def test_rff_energy_grad_matches_oracle(K, fast):
+@pytest.mark.parametrize('kernel,D', [('ffma', 200), ('tc', 200), ('tc', 32), ('tc', 1000), ('tc', 1120)])
+def test_rff_energy_grad_matches_oracle(K, fast, kernel, D):
+    """Both feature kernels (fp32 FFMA; tcgen05 on fp16 hi/lo pairs) against a float64 evaluation.  The feature counts
+    cover a ragged last chunk (200, 1000), a single chunk (32), and odd / even chunk counts with one flush group (7) and
+    several (32, 35)."""
     from qml_lightning_b200 import cabi
     X, Z, c, species = H.batch_mixed(14, seed=K)
-    nel, D = len(species), 200                       # D not a multiple of the 64-feature chunk: ragged last chunk
+    nel = len(species)
     el = torch.tensor(species, dtype=torch.float32, device=DEV)
     g = cabi.group_by_element(Z.to(DEV), c.to(DEV), el)
     gen = torch.Generator().manual_seed(K)
@@ -29,7 +33,13 @@ def test_rff_energy_grad_matches_oracle(K, fast):
     W = torch.randn(nel, K, D, generator=gen) * 0.5
     b = torch.rand(nel, D, generator=gen) * 2 * math.pi
     alpha = torch.randn(D, generator=gen)
-    e_atom, gx = cabi.rff_energy_grad(x.to(DEV), g, W.to(DEV), b.to(DEV), alpha.to(DEV), fast_math=fast)
+    if kernel == 'tc':
+        before = cabi.tc_timeouts()
+        packed = cabi.rff_pack(W.to(DEV), b.to(DEV), alpha.to(DEV))
+        e_atom, gx = cabi.rff_energy_grad_tc(x.to(DEV), g, packed, nel, fast_math=fast)
+        assert cabi.tc_timeouts() == before
+    else:
+        e_atom, gx = cabi.rff_energy_grad(x.to(DEV), g, W.to(DEV), b.to(DEV), alpha.to(DEV), fast_math=fast)
     e_atom, gx = e_atom.cpu().double(), gx.cpu().double()
     gs, sor = g.group_start.cpu(), g.slot_of_row.cpu()
     tol = 3e-5 if fast else 5e-6
@@ -81,3 +91,49 @@ def test_rff_rejects_unsupported_width():
     with pytest.raises(RuntimeError, match='npcas'):
         cabi.rff_energy_grad(torch.zeros(g.rows_cap, 48, device=DEV), g, torch.zeros(3, 48, 64, device=DEV),
                              torch.zeros(3, 64, device=DEV), torch.zeros(64, device=DEV))
+
+
+def test_rff_tc_matches_ffma_on_large_feature_count():
+    """16,384 features (512 chunks, 32 flush groups), wide argument range: the tensor-core kernel stays within fp32
+    rounding of the FFMA kernel and of a float64 evaluation."""
+    from qml_lightning_b200 import cabi
+    X, Z, c, species = H.batch_c1(12)
+    nel, K, D = len(species), 256, 16384
+    g = cabi.group_by_element(Z.to(DEV), c.to(DEV), torch.tensor(species, dtype=torch.float32, device=DEV))
+    gen = torch.Generator().manual_seed(5)
+    x = (torch.randn(g.rows_cap, K, generator=gen) * 0.3).to(DEV)
+    W = (torch.randn(nel, K, D, generator=gen) * 0.5).to(DEV)
+    b = (torch.rand(nel, D, generator=gen) * 2 * math.pi).to(DEV)
+    alpha = torch.randn(D, generator=gen).to(DEV)
+    e0, g0 = cabi.rff_energy_grad(x, g, W, b, alpha, fast_math=True)
+    e1, g1 = cabi.rff_energy_grad_tc(x, g, cabi.rff_pack(W, b, alpha), nel, fast_math=True)
+    used = int(g.group_start[-1])
+    live = (g.slot_of_row[:used] >= 0)
+    gs = g.group_start.cpu()
+    e_ref = torch.zeros(used, dtype=torch.float64, device=DEV)
+    g_ref = torch.zeros(used, K, dtype=torch.float64, device=DEV)
+    for ei in range(nel):
+        r0, r1 = int(gs[ei]), int(gs[ei + 1])
+        arg = x[r0:r1].double() @ W[ei].double() + b[ei].double()
+        a = alpha.double() * math.sqrt(2.0 / D)
+        e_ref[r0:r1] = (torch.cos(arg) * a).sum(-1)
+        g_ref[r0:r1] = -(torch.sin(arg) * a) @ W[ei].double().T
+    se, sg = float(e_ref[live].abs().max()), float(g_ref[live].abs().max())
+    for e, gx in ((e0, g0), (e1, g1)):
+        assert float((e[:used].double() - e_ref)[live].abs().max()) <= 5e-6 * se
+        assert float((gx[:used].double() - g_ref)[live].abs().max()) <= 1e-5 * sg
+    assert (e1[:used][~live] == 0).all() and (g1[:used][~live] == 0).all()
+
+
+def test_rff_tc_refuses_foreign_parameters():
+    """Parameters packed for another npcas: the kernel does nothing and reports through the tensor-core event counter."""
+    from qml_lightning_b200 import cabi
+    X, Z, c, species = H.batch_c0(2)
+    nel = len(species)
+    g = cabi.group_by_element(Z.to(DEV), c.to(DEV), torch.tensor(species, dtype=torch.float32, device=DEV))
+    packed = cabi.rff_pack(torch.zeros(nel, 64, 96, device=DEV), torch.zeros(nel, 96, device=DEV), torch.zeros(96, device=DEV))
+    before = cabi.tc_timeouts()
+    cabi.rff_energy_grad_tc(torch.zeros(g.rows_cap, 128, device=DEV), g, packed, nel)
+    assert cabi.tc_timeouts() > before
+    with pytest.raises(RuntimeError, match='unsupported'):
+        cabi.rff_pack(torch.zeros(nel, 48, 96, device=DEV), torch.zeros(nel, 96, device=DEV), torch.zeros(96, device=DEV))
