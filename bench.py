@@ -10,8 +10,8 @@ and no data-path collective is involved (weak scaling); the reported value is mo
 slowest rank's time.
 
 Prints ONE JSON line.  ``value`` is device-timed with the batch resident in HBM; ``e2e`` goes through the public
-model API from pinned host buffers and back; ``roofline`` covers the dominant kernel (fused SORF energy/gradient)
-timed live with CUDA events; ``cpu_baseline`` is the CPU oracle timed on a bounded sample (rank 0, N = 1 only).
+model API from pinned host buffers and back; ``roofline`` covers the dominant kernel (fused SORF energy/gradient; for
+``--workload c3`` the tensor-core RFF kernel, against the measured dense bf16 rate) timed live with CUDA events; ``cpu_baseline`` is the CPU oracle timed on a bounded sample (rank 0, N = 1 only).
 ``--impl reference`` times the CPU oracle alone (the upstream project has no CPU implementation of this path, so the
 oracle port is the CPU reference).
 """
@@ -36,9 +36,10 @@ WORKLOADS = {
     'c1': ([1, 6, 8], 256, 256, 10000, '21-atom C9H8O4 conformers, weak scaling'),
     'c0': ([1, 6, 8], 128, 128, 1000, '9-atom conformers'),
     'c2': ([1, 6, 7, 8, 9], 128, 256, 200000, 'mixed molecules with 4-29 atoms, sharded over the ranks (strong scaling)'),
+    'c3': ([1, 6, 8], 256, 64, 100000, 'RFF model (dense Gaussian projection, 16,384 features) on the 21-atom conformers, weak scaling'),
     'c4': ([1, 6, 8], 256, 128, 512, 'training normal equations: Z^T Z (fp64, 32768^2) over 21-atom conformers, 64 rows each'),
 }
-KERNELS_PER_STEP = 8  # count, scan, assign, fchl forward, pca (tcgen05), sorf fused, pca^T (tcgen05), fchl backward
+KERNELS_PER_STEP = 8  # count, scan, assign, fchl forward, pca (tcgen05), sorf fused or rff (tcgen05), pca^T (tcgen05), fchl backward
 
 
 def parse_args():
@@ -118,15 +119,20 @@ class ClockSampler:
                 'reasons': sorted(reasons), 'samples': len(sm)}
 
 
-def build_model(device, X, Z, counts, species=SPECIES, npcas=NPCAS, nstacks=NSTACKS):
-    """Model through the public API: FCHLCuda + HadamardFeaturesModel, reductors from SVD of our own representation."""
+def build_model(device, X, Z, counts, species=SPECIES, npcas=NPCAS, nstacks=NSTACKS, kind='sorf'):
+    """Model through the public API: FCHLCuda + HadamardFeaturesModel (or RandomFourrierFeaturesModel), reductors from
+    SVD of our own representation."""
     import qml_lightning_b200 as q
     np.random.seed(1234)
     torch.manual_seed(1234)
     rep = q.FCHLCuda(species=np.array(species), rcut=6.0, nRs2=24, nRs3=22, eta2=0.32, eta3=2.7, two_body_decay=1.8,
                      three_body_weight=13.4, three_body_decay=0.57, device=device)
-    model = q.HadamardFeaturesModel(rep=rep, elements=np.array(species), ntransforms=1, sigma=SIGMA, llambda=1e-5,
-                                    npcas=npcas, nstacks=nstacks, nbatch_train=64, nbatch_test=len(X))
+    if kind == 'rff':
+        model = q.RandomFourrierFeaturesModel(rep=rep, elements=np.array(species), sigma=SIGMA, llambda=1e-5, npcas=npcas,
+                                              nstacks=nstacks, nbatch_train=64, nbatch_test=len(X))
+    else:
+        model = q.HadamardFeaturesModel(rep=rep, elements=np.array(species), ntransforms=1, sigma=SIGMA, llambda=1e-5,
+                                        npcas=npcas, nstacks=nstacks, nbatch_train=64, nbatch_test=len(X))
     nsub = min(len(X), 2048)      # enough atoms of the rarest species for the SVD
     Xl = [X[i, :counts[i]] for i in range(nsub)]
     Zl = [Z[i, :counts[i]] for i in range(nsub)]
@@ -258,9 +264,10 @@ def main():
         X, Z, counts = X[lo:hi], Z[lo:hi], counts[lo:hi]
         nglobal = nreq
     else:
-        X, Z, counts = workload(nreq, 1001 + rank, args.workload)       # every rank owns its own molecules
+        X, Z, counts = workload(nreq, 1001 + rank, 'c1' if args.workload == 'c3' else args.workload)  # every rank owns its own molecules
         nglobal = nreq * world
-    rep, model = build_model(dev, X, Z, counts, species, npcas, nstacks)
+    kind = 'rff' if args.workload == 'c3' else 'sorf'
+    rep, model = build_model(dev, X, Z, counts, species, npcas, nstacks, kind)
     nconf, A = Z.shape
     natoms = int(counts.sum())
     kp = rep.kernel_params(dev)
@@ -272,8 +279,12 @@ def main():
     G = torch.empty(nconf, A, 3, dtype=torch.float32, device=dev)
 
     def step():
-        cabi.sorf_predict(Xd, Zd, cd, kp, model.species, model.reductors, model.packed, nstacks, 1, SIGMA,
-                          n_atoms_upper=natoms, fast_math=model.fast_math, energy=E, grad_X=G)
+        if kind == 'rff':
+            cabi.rff_predict_packed(Xd, Zd, cd, kp, model.species, model.reductors, model.packed, n_atoms_upper=natoms,
+                                    fast_math=model.fast_math, energy=E, grad_X=G)
+        else:
+            cabi.sorf_predict(Xd, Zd, cd, kp, model.species, model.reductors, model.packed, nstacks, 1, SIGMA,
+                              n_atoms_upper=natoms, fast_math=model.fast_math, energy=E, grad_X=G)
 
     for _ in range(args.warmup):
         step()
@@ -307,7 +318,10 @@ def main():
     cabi.fchl19_forward(Xd, Zd, cd, kp, row_of_slot=g.row_of_slot, out=repbuf)
     xproj = cabi.pca_project(repbuf, model.reductors, g)
     def sorf_alone():
-        cabi.sorf_energy_grad(xproj, g, model.packed, npcas, nstacks, 1, SIGMA, model.fast_math)
+        if kind == 'rff':
+            cabi.rff_energy_grad_tc(xproj, g, model.packed, len(species), model.fast_math)
+        else:
+            cabi.sorf_energy_grad(xproj, g, model.packed, npcas, nstacks, 1, SIGMA, model.fast_math)
 
     for _ in range(3):          # warm-up: also lets the caching allocator keep the output blocks
         sorf_alone()
@@ -386,6 +400,18 @@ def main():
                      'peak_source': peak_src, 'kernel_ms': k_ms, 'algorithmic_bytes_per_launch': k_bytes,
                      'pipeline_hbm_equivalent_gbs': pipe_gbs / world, 'pipeline_frac': pipe_gbs / world / hbm},
     }
+    if kind == 'rff':
+        # The dominant kernel is a pair of dense contractions: 2 x (2 npcas D) flops per atom.  `achieved` counts those
+        # algorithmic flops; the tensor cores execute three fp16 products for each (hi*hi + hi*lo + lo*hi).
+        D = npcas * nstacks
+        k_flops = 4.0 * npcas * D * natoms
+        tf = k_flops / (k_ms * 1e-3) / 1e12
+        peak_tf = float(peaks.get('bf16_tflops', 1590.0))
+        line['config']['features'] = D
+        line['roofline'] = {'bound': 'tensor', 'kernel': 'rff_tc_kernel', 'achieved': tf, 'peak': peak_tf, 'unit': 'TFLOP/s',
+                            'frac': tf / peak_tf, 'traffic': None, 'peak_source': peak_src, 'kernel_ms': k_ms,
+                            'algorithmic_flops_per_launch': k_flops, 'issued_mma_tflops': 3.0 * tf,
+                            'issued_frac': 3.0 * tf / peak_tf}
     if world == 1 and not args.no_cpu_baseline and args.workload == 'c1':
         rate, dt = cpu_oracle_rate(model, rep, X, Z, counts, args.cpu_sample)
         line['cpu_baseline'] = {'value': rate, 'unit': 'molecules/s', 'cores': os.cpu_count(), 'kind': 'port',
