@@ -1,5 +1,5 @@
 // Tensor-core version of the fused random-Fourier-feature energy + gradient kernel (tcgen05.mma kind::f16, accumulators
-// in tensor memory, weights streamed by bulk asynchronous copies).
+// and the x operand in tensor memory, weights streamed by bulk asynchronous copies).
 //
 // Per element group the upstream chain (models/random_features.py:98-100 and the autograd backward it builds) is
 //   arg = x W_e + b_e ;  E_row = sum_f a_f cos(arg_f) ;  grad_x = -(a * sin(arg)) W_e^T ,   a = alpha sqrt(2/D).
@@ -8,23 +8,32 @@
 // carries 22 significant bits like a TF32 pair but moves half the bytes and multiplies at twice the rate), and the
 // product is hi*hi + hi*lo + lo*hi accumulated in fp32.
 //
-// One block owns 128 rows of one element group and loops over all features in chunks of 32:
-//   * x (hi, lo) of the tile stays in shared memory for the whole loop (A operand of the first product, K-major);
+// One block (12 warps) owns 128 rows of one element group and loops over all features in chunks of 32:
+//   * x_hi of the tile lives in tensor memory (lane = row, one 32-bit column = two consecutive k) and x_lo in shared
+//     memory (canonical K-major image) for the whole loop;
 //   * the weights are re-packed once per model (qmlb_rff_pack) into per-chunk blobs that already have the shared-memory
-//     image: 8x8 fp16 core matrices [8 k][8 features], blocks ordered (feature block, k block).  The same image is the
-//     B operand of the first product (MN-major: N = features) and of the second (K-major: N = k, K = features), so a
-//     chunk is fetched once, by one cp.async.bulk of 32.4 KB issued by a producer thread, and used twice;
-//   * one thread issues the MMAs: arg chunk (M=128, N=32, K=npcas) into one of two tensor-memory buffers, and
-//     grad (M=128, N=npcas, K=32) into a persistent tensor-memory accumulator;
-//   * four warps (one tensor-memory lane = one row per thread) read the arg chunk, evaluate sin/cos, add the energy
-//     and write G = -a sin(arg) (hi, lo) to shared memory as the A operand of the second product.
-// Chunks are processed in pairs (arg c, arg c+1, grad c, grad c+1) so that the sin/cos work of one chunk hides behind
-// the MMAs of its neighbour and a weight buffer is refilled while the other one is in use.
+//     image: 8x8 fp16 core matrices [8 k][8 features], blocks ordered (feature block, k block), hi image then lo image,
+//     then the chunk's bias and weights.  The same image is the B operand of the first product (MN-major: N = features)
+//     and of the second (K-major: N = k, K = features), so a chunk is fetched once, by one cp.async.bulk of 32.4 KB
+//     issued by a producer thread into a ring of three stages, and used twice;
+//   * first product, per chunk: x_hi [W_hi | W_lo] as npcas/16 MMAs with N = 64 (the lo image continues the hi image at
+//     the feature-block stride, so one descriptor covers both) and x_lo W_hi as npcas/16 MMAs with N = 32, into one of
+//     two 64-column tensor-memory buffers [hi*hi | cross terms].  Issuing an MMA costs tens of cycles whatever its size,
+//     which is more than an N = 32 MMA computes for, so the MMA count is what matters here, and two warps issue: one
+//     the even chunks, one the odd chunks;
+//   * eight warps (warps w and w+4 share the rows of a tensor-memory lane quarter and take 16 features each) read the
+//     arg chunk, evaluate sin/cos, add the energy (compensated sum) and write G = -a sin(arg) (hi, lo) to shared memory
+//     as the A operand of the second product;
+//   * second product, per chunk: 6 MMAs with N = npcas (G_hi W_lo, G_lo W_hi, G_hi W_hi for two 16-feature steps) into
+//     a persistent tensor-memory accumulator, issued by a third warp.
 //
 // The tensor core adds into its fp32 accumulator with truncation (towards zero, up to one ulp of the running sum per
-// MMA).  The small cross terms of the first product are therefore issued first and the hi*hi terms are split over two
-// accumulators; the gradient accumulator is folded into fp32 global memory (round to nearest, red.global.add) every
-// FLUSH_CHUNKS chunks and restarted.
+// MMA).  For arg the small cross terms have their own columns; the gradient accumulator is folded into fp32 global memory
+// (round to nearest, red.global.add) every FLUSH_CHUNKS chunks and restarted (measured relative gradient error
+// 1.9e-6 at 16 chunks, 3.5e-6 at 32, 5.5e-5 without folding over 512 chunks).
+//
+// Tensor memory (all 512 columns): arg 2 x 64, gradient npcas (<= 256), x_hi npcas/2 (<= 128).
+// Shared memory at npcas = 256: x_lo 64 KB, weight ring 3 x 32.4 KB, G 2 x 16 KB.
 //
 // Every wait is bounded.  A thread that times out marks the block as failed; the block then skips its stores, waits
 // (bounded) for its copies and MMAs in flight, releases its tensor memory and counts the event (qmlb_tc_timeouts).
@@ -32,13 +41,18 @@
 #include <cuda_fp16.h>
 #include <math.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace {
 
 constexpr int BM = 128;            // rows per block = QMLB_ROW_TILE
 constexpr int FC = 32;             // features per chunk
-constexpr int NTHREADS = 192;      // warps 0-3: sin/cos + flush, warp 4: MMA issue, warp 5: weight copies
+constexpr int EPI_WARPS = 8;       // warps 0-7: sin/cos + flush (warps w and w+4 share the rows of a tensor-memory lane quarter)
+constexpr int MMA_WARP = 8;        // warp 8: MMAs of the first product for even chunks (+ tensor-memory allocation), warp 9: MMAs
+constexpr int NTHREADS = 384;      // of the second product, warp 10: weight copies, warp 11: first product for odd chunks
+constexpr int NSTAGES = 3;         // weight chunks in flight
 #ifndef QMLB_RFF_FLUSH_CHUNKS
 #define QMLB_RFF_FLUSH_CHUNKS 16
 #endif
@@ -81,13 +95,6 @@ __device__ __forceinline__ void split_half2(float a, float b, __half2 &hi, __hal
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    // start address, leading (K direction) and stride (M/N direction) byte offsets between 8x16-byte core matrices,
-    // all >> 4; descriptor version 1; no swizzle
-    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
-           ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | ((uint64_t)1 << 46);
-}
-
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
@@ -112,34 +119,40 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     }
     return false;
 }
-#ifdef RFF_DBG_PROFILE
-__device__ unsigned long long g_prof[16];
-__device__ __forceinline__ bool mbar_wait_prof(uint32_t bar, uint32_t parity, int slot, bool rec) {
-    const long long t0 = clock64();
-    const bool r = mbar_wait(bar, parity);
-    if (rec) g_prof[slot] += (unsigned long long)(clock64() - t0);
-    return r;
-}
-#define MBAR_WAIT(bar, parity, slot) mbar_wait_prof(bar, parity, slot, blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (threadIdx.x < 32 || threadIdx.x >= 128))
-#define PROF_STAMP(t) const long long t = clock64()
-#define PROF_ADD(slot, t) do { if (blockIdx.x == 0 && threadIdx.x == 0) g_prof[slot] += (unsigned long long)(clock64() - t); } while (0)
-#else
-#define MBAR_WAIT(bar, parity, slot) mbar_wait(bar, parity)
-#define PROF_STAMP(t)
-#define PROF_ADD(slot, t)
-#endif
 __device__ __forceinline__ void bulk_copy(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                  "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(bar)
                  : "memory");
 }
-__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+// A shared-memory descriptor is kept as two 32-bit words so that stepping through an operand is one 32-bit add on the
+// low word (start address >> 4 in bits 0-13, leading byte offset >> 4 in bits 16-29); the high word (stride byte
+// offset >> 4, descriptor version 1 at bit 14, no swizzle) never changes.  The thread that issues the MMAs is
+// instruction bound, so the wrappers keep the per-MMA instruction count minimal.
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) { return ((saddr >> 4) & 0x3FFFu) | ((lbo_bytes >> 4) << 16); }
+__device__ __forceinline__ uint32_t desc_hi(uint32_t sbo_bytes) { return (sbo_bytes >> 4) | (1u << 14); }
+
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint32_t alo, uint32_t ahi, uint32_t blo, uint32_t bhi, uint32_t idesc,
+                                       uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
         :
-        : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "r"(tmem_d), "r"(alo), "r"(ahi), "r"(blo), "r"(bhi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]; A: lane = row, 32-bit column = two consecutive k
+__device__ __forceinline__ void mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t blo, uint32_t bhi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        :
+        : "r"(tmem_d), "r"(tmem_a), "r"(blo), "r"(bhi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
@@ -157,6 +170,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 __device__ __forceinline__ void red_add4(float *p, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&v)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(v[0]), "r"(v[1]),
+                 "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -241,15 +260,24 @@ __global__ void rff_pack_header_kernel(PackHeader *hdr, int K, int D, int nchunk
 // ---------------------------------------------------------------------------------------------------------------
 
 // barrier slots
-enum { W_FULL = 0, W_FREE = 2, ARG_FULL = 4, ARG_FREE = 6, G_FULL = 8, G_FREE = 10, GRAD_FULL = 12, GRAD_FREE = 13, ALL_DONE = 14, NBARS = 15 };
+enum {
+    W_FULL = 0, W_FREE = W_FULL + NSTAGES, ARG_FULL = W_FREE + NSTAGES, ARG_FREE = ARG_FULL + 2, G_FULL = ARG_FREE + 2,
+    G_FREE = G_FULL + 2, GRAD_FULL = G_FREE + 2, GRAD_FREE, ALL_DONE, NBARS
+};
+
+// tensor-memory columns (512 allocated)
+constexpr uint32_t COL_ARG = 0;      // two arg buffers of 2 FC columns: [x_hi W_hi | x_hi W_lo + x_lo W_hi]
+constexpr uint32_t COL_GRAD = 128;   // npcas columns
+constexpr uint32_t COL_XH = 384;     // npcas/2 columns of packed x hi pairs
+constexpr uint32_t TMEM_COLS = 512;
 
 template <int K>
 struct Smem {
-    static constexpr uint32_t X_HALF = BM * K * 2;              // x hi (or lo) image
+    static constexpr uint32_t X_HALF = BM * K * 2;              // x lo image
     static constexpr uint32_t W_HALF = K * FC * 2;              // weight hi (or lo) image of one chunk
     static constexpr uint32_t CHUNK = (uint32_t)chunk_bytes(K);
     static constexpr uint32_t G_HALF = BM * FC * 2;             // G hi (or lo) image
-    static constexpr uint32_t OFF_XH = 0, OFF_XL = X_HALF, OFF_W = 2 * X_HALF, OFF_G = OFF_W + 2 * CHUNK;
+    static constexpr uint32_t OFF_XL = 0, OFF_W = X_HALF, OFF_G = OFF_W + NSTAGES * CHUNK;
     static constexpr uint32_t TOTAL = OFF_G + 4 * G_HALF;
     static_assert(CHUNK % 128 == 0, "chunk images must keep 128-byte alignment");
 };
@@ -260,10 +288,9 @@ rff_tc_kernel(const float *__restrict__ x, const int *__restrict__ group_start, 
               const unsigned char *__restrict__ packed, float *__restrict__ atom_energy, float *__restrict__ grad_x) {
     using S = Smem<K>;
     constexpr int KB = K / 8;
-    constexpr uint32_t TMEM_COLS = 512;
-    constexpr uint32_t COL_GRAD = 128;            // columns 0..127: two arg buffers x two partial accumulators x 32
     extern __shared__ unsigned char smem_dyn[];
     __shared__ __align__(8) uint64_t bars[NBARS];
+    __shared__ float energy_half[BM];
     __shared__ uint32_t tmem_slot;
     __shared__ unsigned xmax_bits;
     __shared__ int failed;
@@ -288,29 +315,24 @@ rff_tc_kernel(const float *__restrict__ x, const int *__restrict__ group_start, 
     auto bar = [&](int i) { return smem_u32(&bars[i]); };
 
     if (tid == 0) {
-        mbar_init(bar(W_FULL), 1); mbar_init(bar(W_FULL + 1), 1);
-        mbar_init(bar(W_FREE), 1); mbar_init(bar(W_FREE + 1), 1);
-        mbar_init(bar(ARG_FULL), 1); mbar_init(bar(ARG_FULL + 1), 1);
-        mbar_init(bar(ARG_FREE), 4); mbar_init(bar(ARG_FREE + 1), 4);
-        mbar_init(bar(G_FULL), 4); mbar_init(bar(G_FULL + 1), 4);
-        mbar_init(bar(G_FREE), 1); mbar_init(bar(G_FREE + 1), 1);
-        mbar_init(bar(GRAD_FULL), 1); mbar_init(bar(GRAD_FREE), 4); mbar_init(bar(ALL_DONE), 1);
+        for (int i = 0; i < NSTAGES; ++i) { mbar_init(bar(W_FULL + i), 1); mbar_init(bar(W_FREE + i), 1); }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar(ARG_FULL + i), 1); mbar_init(bar(ARG_FREE + i), EPI_WARPS);
+            mbar_init(bar(G_FULL + i), EPI_WARPS); mbar_init(bar(G_FREE + i), 1);
+        }
+        mbar_init(bar(GRAD_FULL), 1); mbar_init(bar(GRAD_FREE), EPI_WARPS); mbar_init(bar(ALL_DONE), 3);
         failed = 0;
         xmax_bits = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) {
+    if (warp == MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    __syncthreads();
-
     // the gradient rows of the tile start at zero: the accumulator is folded into them with reductions
     for (int i = tid; i < BM * (K / 4); i += NTHREADS)
         *reinterpret_cast<float4 *>(grad_x + (size_t)row0 * K + (size_t)i * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
-
-    // ---- x tile: scale, split, canonical K-major image (8 rows x 8 k core matrices, k blocks outermost) ----
-    {
+    {   // largest |x| of the tile -> power-of-two scale
         float m = 0.f;
         for (int i = tid; i < BM * (K / 4); i += NTHREADS) {
             const int r = i / (K / 4), k4 = (i % (K / 4)) * 4;
@@ -321,111 +343,126 @@ rff_tc_kernel(const float *__restrict__ x, const int *__restrict__ group_start, 
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(QMLB_FULL_MASK, m, o));
+        __syncthreads();   // xmax_bits initialised
         if (lane == 0 && m < INFINITY) atomicMax(&xmax_bits, __float_as_uint(m));
     }
+    fence_before();
     __syncthreads();
+    fence_after();
+    // All 512 columns are allocated, so the allocation can only start at column 0 (checked): tensor-memory addresses are
+    // then compile-time constants, which keeps them out of the per-MMA instruction stream.
+    const uint32_t tmem_alloc = tmem_slot;
+    constexpr uint32_t tmem = 0u;
+    const bool tmem_ok = tmem_alloc == 0u;
     const int ex = exponent_of(xmax_bits);
-    {
-        const float sx = pow2i(13 - ex);
-        for (int i = tid; i < BM * KB; i += NTHREADS) {
-            const int r = i % BM, kb = i / BM;
-            __align__(16) __half hi[8], lo[8];
-            float v[8];
-            if (slot_of_row[row0 + r] >= 0) {
-                const float4 a = *reinterpret_cast<const float4 *>(x + (size_t)(row0 + r) * K + kb * 8);
-                const float4 c = *reinterpret_cast<const float4 *>(x + (size_t)(row0 + r) * K + kb * 8 + 4);
-                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = c.x; v[5] = c.y; v[6] = c.z; v[7] = c.w;
-            } else {
+    const float sx = pow2i(13 - ex);
+
+    // ---- x lo: canonical K-major shared-memory image (8 rows x 8 k core matrices, k blocks outermost) ----
+    for (int i = tid; i < BM * KB; i += NTHREADS) {
+        const int r = i % BM, kb = i / BM;
+        __align__(16) __half2 lo[4];
+        if (slot_of_row[row0 + r] >= 0) {
+            const float4 a = *reinterpret_cast<const float4 *>(x + (size_t)(row0 + r) * K + kb * 8);
+            const float4 c = *reinterpret_cast<const float4 *>(x + (size_t)(row0 + r) * K + kb * 8 + 4);
+            __half2 hi;
+            split_half2(a.x * sx, a.y * sx, hi, lo[0]);
+            split_half2(a.z * sx, a.w * sx, hi, lo[1]);
+            split_half2(c.x * sx, c.y * sx, hi, lo[2]);
+            split_half2(c.z * sx, c.w * sx, hi, lo[3]);
+        } else {
 #pragma unroll
-                for (int q = 0; q < 8; ++q) v[q] = 0.f;
-            }
-#pragma unroll
-            for (int q = 0; q < 8; ++q) split_half(v[q] * sx, hi[q], lo[q]);
-            const uint32_t off = (uint32_t)(kb * 16 + (r >> 3)) * 128u + (uint32_t)(r & 7) * 16u;
-            *reinterpret_cast<uint4 *>(sptr + S::OFF_XH + off) = *reinterpret_cast<const uint4 *>(hi);
-            *reinterpret_cast<uint4 *>(sptr + S::OFF_XL + off) = *reinterpret_cast<const uint4 *>(lo);
+            for (int q = 0; q < 4; ++q) lo[q] = __floats2half2_rn(0.f, 0.f);
         }
+        const uint32_t off = (uint32_t)(kb * 16 + (r >> 3)) * 128u + (uint32_t)(r & 7) * 16u;
+        *reinterpret_cast<uint4 *>(sptr + S::OFF_XL + off) = *reinterpret_cast<const uint4 *>(lo);
+    }
+    // ---- x hi: tensor memory, lane = row, column j = (k = 2j, k = 2j + 1) packed; warps w and w + 4 share a lane quarter
+    if (warp < EPI_WARPS && tmem_ok) {
+        const int r = (warp & 3) * 32 + lane, h = warp >> 2;
+        const bool live = slot_of_row[row0 + r] >= 0;
+        const uint32_t lane_field = (uint32_t)((warp & 3) * 32) << 16;
+        const float *xr = x + (size_t)(row0 + r) * K + h * (K / 2);
+#pragma unroll 1
+        for (int j = 0; j < K / 32; ++j) {      // 16 k = 8 columns per store
+            uint32_t pk[8];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (live) v = *reinterpret_cast<const float4 *>(xr + j * 16 + q * 4);
+                __half2 h0, h1, l0;
+                split_half2(v.x * sx, v.y * sx, h0, l0);
+                split_half2(v.z * sx, v.w * sx, h1, l0);
+                pk[2 * q] = *reinterpret_cast<uint32_t *>(&h0);
+                pk[2 * q + 1] = *reinterpret_cast<uint32_t *>(&h1);
+            }
+            tmem_st8(tmem + lane_field + COL_XH + (uint32_t)(h * (K / 4) + j * 8), pk);
+        }
+        tmem_st_wait();
     }
     fence_async_smem();
     fence_before();
     __syncthreads();
     fence_after();
-    const uint32_t tmem = tmem_slot;
     const float arg_scale = pow2i(ex - 13) * pow2i(ew - 13);     // undoes the operand scales of the first product
     const float grad_scale = pow2i(ea - 13) * pow2i(ew - 13);    // and of the second
 
-#ifdef RFF_DBG_PROFILE
-    const long long t_role0 = clock64();
-#endif
-    if (warp < 4) {
-        // ------------------------------------------------------------------ sin/cos warps: one row per thread
-        const int r = warp * 32 + lane;
+    if (warp < EPI_WARPS) {
+        // ------------------------------------------------------------------ sin/cos warps
+        // thread = (row r, half h): features [16 h, 16 h + 16) of every chunk, gradient columns [h K/2, (h+1) K/2)
+        const int r = (warp & 3) * 32 + lane, h = warp >> 2;
         const bool live = slot_of_row[row0 + r] >= 0;
-        const uint32_t lane_field = (uint32_t)(warp * 32) << 16;
-        const uint32_t g_off = (uint32_t)(r >> 3) * 128u + (uint32_t)(r & 7) * 16u;
+        const uint32_t lane_field = (uint32_t)((warp & 3) * 32) << 16;
         float eacc = 0.f, ecomp = 0.f;  // energy of the row, summed over the chunks with compensation
-        bool ok = true;
+        bool ok = tmem_ok;
         for (int c = 0; c < nchunks && ok; ++c) {
-            const int s = c & 1;
+            const int b = c & 1, s = c % NSTAGES;
             const uint32_t par = (uint32_t)(c >> 1) & 1u;
-            if (!MBAR_WAIT(bar(ARG_FULL + s), par, 0)) { ok = false; break; }
+            if (!mbar_wait(bar(ARG_FULL + b), par)) { ok = false; break; }
             fence_after();
-            PROF_STAMP(t0);
-            float arg[FC];
-#pragma unroll
-            for (int h = 0; h < FC / 16; ++h) {
-                uint32_t v0[16], v1[16];
-                tmem_ld16(tmem + lane_field + (uint32_t)(s * 64 + h * 16), v0);
-                tmem_ld16(tmem + lane_field + (uint32_t)(s * 64 + 32 + h * 16), v1);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 16; ++i) arg[h * 16 + i] = __uint_as_float(v0[i]) + __uint_as_float(v1[i]);
-            }
+            uint32_t av[16], cv[16];   // hi*hi block and cross-term block of this thread's 16 features
+            tmem_ld16(tmem + lane_field + COL_ARG + (uint32_t)(b * 2 * FC + h * 16), av);
+            tmem_ld16(tmem + lane_field + COL_ARG + (uint32_t)(b * 2 * FC + FC + h * 16), cv);
+            tmem_ld_wait();
             fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(ARG_FREE + s));
-            PROF_ADD(12, t0);
+            if (lane == 0) mbar_arrive(bar(ARG_FREE + b));
             // the chunk image (already complete: the MMAs above read it) also carries this chunk's bias and weights;
             // observing its barrier makes the copied bytes visible to this thread's loads
-            if (!MBAR_WAIT(bar(W_FULL + s), par, 1)) { ok = false; break; }
-            const float *prm = reinterpret_cast<const float *>(sptr + S::OFF_W + s * S::CHUNK + 2 * S::W_HALF);
-            // the previous use of this G buffer (chunk c-2) must have been consumed by its MMAs
-            if (c >= 2 && !MBAR_WAIT(bar(G_FREE + s), (uint32_t)((c >> 1) - 1) & 1u, 2)) { ok = false; break; }
-            unsigned char *gbuf = sptr + S::OFF_G + s * 2 * S::G_HALF;
+            if (!mbar_wait(bar(W_FULL + s), (uint32_t)(c / NSTAGES) & 1u)) { ok = false; break; }
+            const float *prm = reinterpret_cast<const float *>(sptr + S::OFF_W + s * S::CHUNK + 2 * S::W_HALF) + h * 16;
             float echunk = 0.f;
-            PROF_STAMP(t1);
+            uint32_t ghi[8], glo[8];
 #pragma unroll
-            for (int fb = 0; fb < FC / 8; ++fb) {
-                __align__(16) __half2 hi[4], lo[4];
+            for (int q = 0; q < 8; ++q) {
+                float gq[2];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    float gq[2];
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const int f = fb * 8 + 2 * q + h;
-                        const float a = fmaf(arg[f], arg_scale, prm[f]);
-                        float sn, cs;
-#ifdef RFF_DBG_NO_SINCOS
-                        sn = a; cs = a;
-#else
-                        if (FAST) __sincosf(a, &sn, &cs);
-                        else sincosf(a, &sn, &cs);
-#endif
-                        echunk = fmaf(prm[FC + f], cs, echunk);
-                        gq[h] = prm[2 * FC + f] * sn;
-                    }
-                    split_half2(gq[0], gq[1], hi[q], lo[q]);
+                for (int t = 0; t < 2; ++t) {
+                    const int f = 2 * q + t;
+                    const float a = fmaf(__uint_as_float(av[f]) + __uint_as_float(cv[f]), arg_scale, prm[f]);
+                    float sn, cs;
+                    if (FAST) __sincosf(a, &sn, &cs);
+                    else sincosf(a, &sn, &cs);
+                    echunk = fmaf(prm[FC + f], cs, echunk);
+                    gq[t] = prm[2 * FC + f] * sn;
                 }
-                const uint32_t off = (uint32_t)fb * (16u * 128u) + g_off;
-                *reinterpret_cast<uint4 *>(gbuf + off) = *reinterpret_cast<const uint4 *>(hi);
-                *reinterpret_cast<uint4 *>(gbuf + S::G_HALF + off) = *reinterpret_cast<const uint4 *>(lo);
+                __half2 hi, lo;
+                split_half2(gq[0], gq[1], hi, lo);
+                ghi[q] = *reinterpret_cast<uint32_t *>(&hi);
+                glo[q] = *reinterpret_cast<uint32_t *>(&lo);
             }
-            PROF_ADD(13, t1);
-            PROF_STAMP(t2);
+            // the previous use of this G buffer (chunk c-2) must have been consumed by its MMAs
+            if (c >= 2 && !mbar_wait(bar(G_FREE + b), (uint32_t)((c >> 1) - 1) & 1u)) { ok = false; break; }
+            {   // canonical K-major image (K = features): 8 rows x 8 features per 128-byte core matrix, feature blocks outermost
+                unsigned char *gbuf = sptr + S::OFF_G + b * 2 * S::G_HALF;
+                const uint32_t off = (uint32_t)(2 * h) * 2048u + (uint32_t)(r >> 3) * 128u + (uint32_t)(r & 7) * 16u;
+                *reinterpret_cast<uint4 *>(gbuf + off) = make_uint4(ghi[0], ghi[1], ghi[2], ghi[3]);
+                *reinterpret_cast<uint4 *>(gbuf + off + 2048u) = make_uint4(ghi[4], ghi[5], ghi[6], ghi[7]);
+                *reinterpret_cast<uint4 *>(gbuf + S::G_HALF + off) = make_uint4(glo[0], glo[1], glo[2], glo[3]);
+                *reinterpret_cast<uint4 *>(gbuf + S::G_HALF + off + 2048u) = make_uint4(glo[4], glo[5], glo[6], glo[7]);
+            }
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(G_FULL + s));
-            PROF_ADD(14, t2);
+            if (lane == 0) mbar_arrive(bar(G_FULL + b));
             {   // Kahan step: a plain running sum over nfeatures terms would lose ~sqrt(nfeatures) ulps
                 const float y = echunk - ecomp, t = eacc + y;
                 ecomp = (t - eacc) - y;
@@ -435,122 +472,138 @@ rff_tc_kernel(const float *__restrict__ x, const int *__restrict__ group_start, 
             if ((c % FLUSH_CHUNKS) == FLUSH_CHUNKS - 1 || c == nchunks - 1) {
                 // fold the gradient accumulator of this group into global memory
                 const int group = c / FLUSH_CHUNKS;
-                if (!MBAR_WAIT(bar(GRAD_FULL), (uint32_t)group & 1u, 3)) { ok = false; break; }
+                if (!mbar_wait(bar(GRAD_FULL), (uint32_t)group & 1u)) { ok = false; break; }
                 fence_after();
-                PROF_STAMP(t3);
-                float *dst = grad_x + (size_t)(row0 + r) * K;
+                float *dst = grad_x + (size_t)(row0 + r) * K + h * (K / 2);
 #pragma unroll 1
-                for (int cc = 0; cc < K; cc += 32) {
-                    uint32_t v0[16], v1[16];
-                    tmem_ld16(tmem + lane_field + COL_GRAD + (uint32_t)cc, v0);
-                    tmem_ld16(tmem + lane_field + COL_GRAD + (uint32_t)cc + 16u, v1);
+                for (int cc = 0; cc < K / 2; cc += 16) {
+                    uint32_t v0[16];
+                    tmem_ld16(tmem + lane_field + COL_GRAD + (uint32_t)(h * (K / 2) + cc), v0);
                     tmem_ld_wait();
                     if (live) {  // rows of the padding keep their zeros
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
+                        for (int q = 0; q < 4; ++q)
                             red_add4(dst + cc + 4 * q, __uint_as_float(v0[4 * q]) * grad_scale, __uint_as_float(v0[4 * q + 1]) * grad_scale,
                                      __uint_as_float(v0[4 * q + 2]) * grad_scale, __uint_as_float(v0[4 * q + 3]) * grad_scale);
-                            red_add4(dst + cc + 16 + 4 * q, __uint_as_float(v1[4 * q]) * grad_scale, __uint_as_float(v1[4 * q + 1]) * grad_scale,
-                                     __uint_as_float(v1[4 * q + 2]) * grad_scale, __uint_as_float(v1[4 * q + 3]) * grad_scale);
-                        }
                     }
                 }
                 fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(GRAD_FREE));
-                PROF_ADD(15, t3);
             }
         }
-        if (ok) atom_energy[row0 + r] = live ? eacc : 0.f;
-        else failed = 1;  // benign race: every writer stores 1
-    } else if (warp == 4) {
-        // ------------------------------------------------------------------ MMA issue
-        if (lane == 0) {
-            // D = F32, A = B = F16; first product: A K-major, B MN-major, N = FC; second: both K-major, N = K
-            const uint32_t idesc1 = (1u << 4) | (1u << 16) | ((uint32_t)(FC >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-            const uint32_t idesc2 = (1u << 4) | ((uint32_t)(K >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-            const uint32_t xh = sbase + S::OFF_XH, xl = sbase + S::OFF_XL;
-            bool ok = true;
-            auto issue_arg = [&](int c) {
-                const int s = c & 1;
-                if (!MBAR_WAIT(bar(W_FULL + s), (uint32_t)(c >> 1) & 1u, 5)) { ok = false; return; }
-                if (c >= 2 && !MBAR_WAIT(bar(ARG_FREE + s), (uint32_t)((c >> 1) - 1) & 1u, 6)) { ok = false; return; }
+        if (!ok) failed = 1;  // benign race: every writer stores 1
+        // the two halves of a row add their energies through shared memory
+        if (h == 1) energy_half[r] = eacc;
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+        if (h == 0 && ok) atom_energy[row0 + r] = live ? eacc + energy_half[r] : 0.f;
+    } else if (warp == MMA_WARP || warp == MMA_WARP + 3) {
+        // ------------------------------------------------------------------ MMAs of the first product: arg = x W
+        // Issuing an MMA costs a thread several tens of cycles whatever the MMA's size, and an N = 32 MMA computes for 16,
+        // so (a) the count is kept low: x_hi multiplies [W_hi | W_lo] in one N = 2 FC instruction (the lo image follows
+        // the hi image at the feature-block stride) and x_lo multiplies W_hi with N = FC into the cross-term columns;
+        // (b) two warps issue, one the even chunks (arg buffer 0), one the odd chunks (arg buffer 1); (c) the whole warp
+        // runs the loop in uniform control flow and only the MMA and commit instructions are left to lane 0, so that
+        // descriptors and addresses are warp-uniform values.
+        // D = F32, A = B = F16, A K-major, B MN-major (N = features)
+        constexpr uint32_t idesc_wide = (1u << 4) | (1u << 16) | ((uint32_t)((2 * FC) >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+        constexpr uint32_t idesc_one = (1u << 4) | (1u << 16) | ((uint32_t)(FC >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+        static_assert(Smem<K>::W_HALF == (uint32_t)(FC / 8) * KB * 128u, "the lo image must continue the feature-block stride");
+        // A from shared memory: 16 k per step = 2 k blocks 2048 B apart, row groups 128 B apart; from tensor memory:
+        // 8 columns per step.  B: 2 k blocks 128 B apart, feature blocks KB*128 B apart
+        const uint32_t a_lo = desc_lo(sbase + S::OFF_XL, 2048u);
+        constexpr uint32_t a_hi = (128u >> 4) | (1u << 14), b_hi = (((uint32_t)KB * 128u) >> 4) | (1u << 14);
+        constexpr uint32_t xh = tmem + COL_XH;
+        bool ok = tmem_ok;
+        auto chunks_of_parity = [&](auto parity) {
+            constexpr int b = decltype(parity)::value;
+            constexpr uint32_t acc = tmem + COL_ARG + (uint32_t)(b * 2 * FC);
+            for (int c = b; c < nchunks && ok; c += 2) {
+                const int s = c % NSTAGES;
+                bool w = mbar_wait(bar(W_FULL + s), (uint32_t)(c / NSTAGES) & 1u);
+                // arg chunks run up to two ahead of the sin/cos warps
+                if (c >= 2) w = mbar_wait(bar(ARG_FREE + b), (uint32_t)((c >> 1) - 1) & 1u) && w;
+                if (!__all_sync(QMLB_FULL_MASK, w)) { ok = false; break; }
                 fence_after();
-                const uint32_t wh = sbase + S::OFF_W + s * S::CHUNK, wl = wh + S::W_HALF;
-                const uint32_t acc0 = tmem + (uint32_t)(s * 64), acc1 = acc0 + 32;
-                // A: 16 k per step = 2 k blocks of 2048 B; B: 2 k blocks of 128 B
-                auto adesc = [&](uint32_t base, int ks) { return make_desc(base + (uint32_t)ks * 4096u, 2048u, 128u); };
-                auto bdesc = [&](uint32_t base, int ks) { return make_desc(base + (uint32_t)ks * 256u, 128u, (uint32_t)KB * 128u); };
-#ifndef RFF_DBG_NO_CROSS1
-                for (int ks = 0; ks < K / 16; ++ks) mma_f16(acc0, adesc(xh, ks), bdesc(wl, ks), idesc1, ks > 0 ? 1u : 0u);
-                for (int ks = 0; ks < K / 16; ++ks) mma_f16(acc0, adesc(xl, ks), bdesc(wh, ks), idesc1, 1u);
-#endif
-                for (int ks = 0; ks < K / 32; ++ks) mma_f16(acc0, adesc(xh, ks), bdesc(wh, ks), idesc1, 1u);
-                for (int ks = K / 32; ks < K / 16; ++ks) mma_f16(acc1, adesc(xh, ks), bdesc(wh, ks), idesc1, ks > K / 32 ? 1u : 0u);
-                mma_commit(bar(ARG_FULL + s));
-            };
-            auto issue_grad = [&](int c) {
-                const int s = c & 1;
-                if (!MBAR_WAIT(bar(G_FULL + s), (uint32_t)(c >> 1) & 1u, 7)) { ok = false; return; }
-                const int group = c / FLUSH_CHUNKS;
-                const bool first = (c % FLUSH_CHUNKS) == 0;
-                if (first && group > 0 && !MBAR_WAIT(bar(GRAD_FREE), (uint32_t)(group - 1) & 1u, 8)) { ok = false; return; }
-                fence_after();
-                const uint32_t wh = sbase + S::OFF_W + s * S::CHUNK, wl = wh + S::W_HALF;
-                const uint32_t gh = sbase + S::OFF_G + s * 2 * S::G_HALF, gl = gh + S::G_HALF;
-                // A: 16 features per step = 2 feature blocks of 2048 B; B: 2 feature blocks of KB*128 B
-                auto adesc = [&](uint32_t base, int ks) { return make_desc(base + (uint32_t)ks * 4096u, 2048u, 128u); };
-                auto bdesc = [&](uint32_t base, int ks) { return make_desc(base + (uint32_t)ks * 2u * KB * 128u, (uint32_t)KB * 128u, 128u); };
-#ifndef RFF_DBG_NO_GRAD
-                for (int ks = 0; ks < FC / 16; ++ks) {
-                    mma_f16(tmem + COL_GRAD, adesc(gh, ks), bdesc(wl, ks), idesc2, (first && ks == 0) ? 0u : 1u);
-                    mma_f16(tmem + COL_GRAD, adesc(gl, ks), bdesc(wh, ks), idesc2, 1u);
-                    mma_f16(tmem + COL_GRAD, adesc(gh, ks), bdesc(wh, ks), idesc2, 1u);
+                const uint32_t wh_lo = desc_lo(sbase + S::OFF_W + s * S::CHUNK, 128u);
+                if (lane == 0) {
+#pragma unroll
+                    for (int ks = 0; ks < K / 16; ++ks) mma_ts(acc, xh + ks * 8, wh_lo + ks * 16, b_hi, idesc_wide, ks > 0 ? 1u : 0u);
+#pragma unroll
+                    for (int ks = 0; ks < K / 16; ++ks) mma_ss(acc + FC, a_lo + ks * 256, a_hi, wh_lo + ks * 16, b_hi, idesc_one, 1u);
+                    mma_commit(bar(ARG_FULL + b));
                 }
-#endif
-                mma_commit(bar(W_FREE + s));
-                mma_commit(bar(G_FREE + s));
-                if ((c % FLUSH_CHUNKS) == FLUSH_CHUNKS - 1 || c == nchunks - 1) mma_commit(bar(GRAD_FULL));
-            };
-            for (int c0 = 0; c0 < nchunks && ok; c0 += 2) {
-                issue_arg(c0);
-                if (ok && c0 + 1 < nchunks) issue_arg(c0 + 1);
-                if (ok) issue_grad(c0);
-                if (ok && c0 + 1 < nchunks) issue_grad(c0 + 1);
+                __syncwarp();
             }
-            // everything issued so far must have left the tensor pipe before the tensor memory is released
-            mma_commit(bar(ALL_DONE));
-            if (!mbar_wait(bar(ALL_DONE), 0u)) ok = false;
-            if (!ok) failed = 1;
+        };
+        if (warp == MMA_WARP) chunks_of_parity(std::integral_constant<int, 0>{});
+        else chunks_of_parity(std::integral_constant<int, 1>{});
+        // everything issued by this warp must have left the tensor pipe before the tensor memory is released
+        if (lane == 0) mma_commit(bar(ALL_DONE));
+        __syncwarp();
+        if (!mbar_wait(bar(ALL_DONE), 0u)) ok = false;
+        if (!ok) failed = 1;
+    } else if (warp == MMA_WARP + 1) {
+        // ------------------------------------------------------------------ MMAs of the second product: grad += G W^T
+        // both operands K-major (K = features), N = npcas; A = G: 16 features per step = 2 feature blocks 2048 B apart,
+        // row groups 128 B apart; B: 2 feature blocks KB*128 B apart, k blocks 128 B apart
+        constexpr uint32_t idesc2 = (1u << 4) | ((uint32_t)(K >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+        constexpr uint32_t ab_hi = (128u >> 4) | (1u << 14);
+        constexpr uint32_t grad = tmem + COL_GRAD;
+        bool ok = tmem_ok;
+        for (int c = 0; c < nchunks && ok; ++c) {
+            const int s = c % NSTAGES, b = c & 1;
+            const int group = c / FLUSH_CHUNKS;
+            const bool first = (c % FLUSH_CHUNKS) == 0;
+            bool w = mbar_wait(bar(G_FULL + b), (uint32_t)(c >> 1) & 1u);
+            if (first && group > 0) w = mbar_wait(bar(GRAD_FREE), (uint32_t)(group - 1) & 1u) && w;
+            if (!__all_sync(QMLB_FULL_MASK, w)) { ok = false; break; }
+            fence_after();
+            const uint32_t wh_lo = desc_lo(sbase + S::OFF_W + s * S::CHUNK, (uint32_t)KB * 128u), wl_lo = wh_lo + (S::W_HALF >> 4);
+            const uint32_t gh_lo = desc_lo(sbase + S::OFF_G + b * 2 * S::G_HALF, 2048u), gl_lo = gh_lo + (S::G_HALF >> 4);
+            if (lane == 0) {
+#pragma unroll
+                for (int ks = 0; ks < FC / 16; ++ks) {
+                    const uint32_t step = (uint32_t)ks * ((2u * KB * 128u) >> 4);
+                    mma_ss(grad, gh_lo + ks * 256, ab_hi, wl_lo + step, ab_hi, idesc2, (first && ks == 0) ? 0u : 1u);
+                    mma_ss(grad, gl_lo + ks * 256, ab_hi, wh_lo + step, ab_hi, idesc2, 1u);
+                    mma_ss(grad, gh_lo + ks * 256, ab_hi, wh_lo + step, ab_hi, idesc2, 1u);
+                }
+                mma_commit(bar(W_FREE + s));
+                mma_commit(bar(G_FREE + b));
+                if ((c % FLUSH_CHUNKS) == FLUSH_CHUNKS - 1 || c == nchunks - 1) mma_commit(bar(GRAD_FULL));
+            }
+            __syncwarp();
         }
-    } else {
+        if (lane == 0) mma_commit(bar(ALL_DONE));
+        __syncwarp();
+        if (!mbar_wait(bar(ALL_DONE), 0u)) ok = false;
+        if (!ok) failed = 1;
+    } else if (warp == MMA_WARP + 2) {
         // ------------------------------------------------------------------ weight copies
         if (lane == 0) {
-            bool ok = true;
+            bool ok = tmem_ok;
             int issued = 0;
-            for (int c = 0; c < nchunks; ++c) {
-                const int s = c & 1;
-                if (c >= 2 && !MBAR_WAIT(bar(W_FREE + s), (uint32_t)((c >> 1) - 1) & 1u, 10)) { ok = false; break; }
+            for (int c = 0; c < nchunks && ok; ++c) {
+                const int s = c % NSTAGES;
+                if (c >= NSTAGES && !mbar_wait(bar(W_FREE + s), (uint32_t)((c / NSTAGES) - 1) & 1u)) { ok = false; break; }
                 mbar_expect_tx(bar(W_FULL + s), S::CHUNK);
                 bulk_copy(sbase + S::OFF_W + s * S::CHUNK, blobs + (size_t)c * S::CHUNK, S::CHUNK, bar(W_FULL + s));
                 issued = c + 1;
             }
             // no copy may still be in flight when the block leaves
-            for (int c = max(0, issued - 2); c < issued; ++c)
-                if (!mbar_wait(bar(W_FULL + (c & 1)), (uint32_t)(c >> 1) & 1u)) ok = false;
+            for (int c = max(0, issued - NSTAGES); c < issued; ++c)
+                if (!mbar_wait(bar(W_FULL + (c % NSTAGES)), (uint32_t)(c / NSTAGES) & 1u)) ok = false;
             if (!ok) failed = 1;
         }
     }
-#ifdef RFF_DBG_PROFILE
-    if (blockIdx.x == 0 && lane == 0 && (warp == 0 || warp >= 4)) g_prof[warp == 0 ? 4 : (warp == 4 ? 9 : 11)] += (unsigned long long)(clock64() - t_role0);
-#endif
     __syncwarp();
     fence_before();
     __syncthreads();
     fence_after();
     if (failed && tid == 0) atomicAdd(&g_rff_tc_timeouts, 1);
-    if (warp == 4) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    if (warp == MMA_WARP) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_alloc), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -589,13 +642,6 @@ int launch_rff_pack(const float *W, const float *b, const float *alpha, int nel,
 bool supported_npcas(int npcas) { return npcas == 32 || npcas == 64 || npcas == 128 || npcas == 256; }
 
 }  // namespace
-
-#ifdef RFF_DBG_PROFILE
-extern "C" int qmlb_dbg_rff_profile(unsigned long long *out, int reset) {
-    if (reset) { unsigned long long z[16] = {}; return cudaMemcpyToSymbol(g_prof, z, sizeof(z)) != cudaSuccess; }
-    return cudaMemcpyFromSymbol(out, g_prof, 16 * sizeof(unsigned long long)) != cudaSuccess;
-}
-#endif
 
 namespace qmlb {
 int rff_tc_timeouts() {
