@@ -411,7 +411,9 @@ def main():
         line['roofline'] = {'bound': 'tensor', 'kernel': 'rff_tc_kernel', 'achieved': tf, 'peak': peak_tf, 'unit': 'TFLOP/s',
                             'frac': tf / peak_tf, 'traffic': None, 'peak_source': peak_src, 'kernel_ms': k_ms,
                             'algorithmic_flops_per_launch': k_flops, 'issued_mma_tflops': 3.0 * tf,
-                            'issued_frac': 3.0 * tf / peak_tf}
+                            'issued_frac': 3.0 * tf / peak_tf,
+                            # whole step: both PCA products and both RFF products, 2 (2 repsize npcas) + 2 (2 npcas D) per atom
+                            'pipeline_tflops': (4.0 * rep.get_repsize() * npcas + 4.0 * npcas * D) * natoms / (ms_max * 1e-3) / 1e12}
     if world == 1 and not args.no_cpu_baseline and args.workload == 'c1':
         rate, dt = cpu_oracle_rate(model, rep, X, Z, counts, args.cpu_sample)
         line['cpu_baseline'] = {'value': rate, 'unit': 'molecules/s', 'cores': os.cpu_count(), 'kind': 'port',

@@ -137,3 +137,33 @@ def test_rff_tc_refuses_foreign_parameters():
     assert cabi.tc_timeouts() > before
     with pytest.raises(RuntimeError, match='unsupported'):
         cabi.rff_pack(torch.zeros(nel, 48, 96, device=DEV), torch.zeros(nel, 96, device=DEV), torch.zeros(96, device=DEV))
+
+
+@pytest.mark.parametrize('xscale,ascale', [(1e-6, 1.0), (3e3, 1e-4), (1.0, 1e5)])
+def test_rff_tc_operand_scaling(xscale, ascale):
+    """The fp16 hi/lo pairs are formed after power-of-two scaling of x (per row tile), W and alpha (per model), so
+    tiny / large inputs and weights keep fp32-level accuracy; alpha additionally spans six orders of magnitude."""
+    from qml_lightning_b200 import cabi
+    X, Z, c, species = H.batch_c0(20)
+    nel, K, D = len(species), 64, 512
+    g = cabi.group_by_element(Z.to(DEV), c.to(DEV), torch.tensor(species, dtype=torch.float32, device=DEV))
+    gen = torch.Generator().manual_seed(11)
+    x = (torch.randn(g.rows_cap, K, generator=gen) * xscale).to(DEV)
+    W = (torch.randn(nel, K, D, generator=gen) * (0.3 / xscale)).to(DEV)       # arguments stay of order one
+    b = (torch.rand(nel, D, generator=gen) * 2 * math.pi).to(DEV)
+    alpha = (torch.randn(D, generator=gen) * ascale * torch.logspace(-6, 0, D)).to(DEV)
+    e1, g1 = cabi.rff_energy_grad_tc(x, g, cabi.rff_pack(W, b, alpha), nel, fast_math=False)
+    used = int(g.group_start[-1])
+    live = g.slot_of_row[:used] >= 0
+    gs = g.group_start.cpu()
+    a = alpha.double() * math.sqrt(2.0 / D)
+    for ei in range(nel):
+        r0, r1 = int(gs[ei]), int(gs[ei + 1])
+        arg = x[r0:r1].double() @ W[ei].double() + b[ei].double()
+        e_ref = (torch.cos(arg) * a).sum(-1)
+        g_ref = -(torch.sin(arg) * a) @ W[ei].double().T
+        lv = live[r0:r1]
+        if not bool(lv.any()):
+            continue
+        assert float((e1[r0:r1].double() - e_ref)[lv].abs().max()) <= 5e-6 * float(e_ref[lv].abs().max())
+        assert float((g1[r0:r1].double() - g_ref)[lv].abs().max()) <= 1e-5 * float(g_ref[lv].abs().max())
