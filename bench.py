@@ -215,12 +215,18 @@ def run_training(args, rank, world, local):
     model.allreduce_normal_equations(ZTZ, ZTy)
     torch.cuda.synchronize()
     t_red = time.perf_counter() - t1
-    tt = torch.tensor([t_acc, t_red], dtype=torch.float64, device=dev)
+    t2 = time.perf_counter()
+    alpha = model.solve_normal_equations(ZTZ, ZTy)      # replicated on every rank
+    torch.cuda.synchronize()
+    t_solve = time.perf_counter() - t2
+    solved = bool(torch.isfinite(alpha).all())
+    del ZTZ
+    tt = torch.tensor([t_acc, t_red, t_solve], dtype=torch.float64, device=dev)
     if dist is not None:
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
     if rank == 0:
         F = npcas * nstacks
-        t_acc, t_red = float(tt[0]), float(tt[1])
+        t_acc, t_red, t_solve = float(tt[0]), float(tt[1]), float(tt[2])
         flops = 2.0 * 64 * F * F * n * world          # algorithmic: full Z^T Z product per conformer
         print(json.dumps({
             'metric': 'normal-equation accumulation', 'value': n * world / t_acc, 'unit': 'conformers/s', 'n_gpus': world,
@@ -228,7 +234,8 @@ def run_training(args, rank, world, local):
             'dtype': 'f64', 'data': 'synthetic',
             'config': {'workload': 'c4', 'conformers_per_gpu': n, 'rows_per_conformer': 64, 'features': F, 'nbatch_train': 64},
             'fp64_algorithmic_tflops': flops / t_acc / 1e12, 'allreduce_ms': t_red * 1e3,
-            'allreduce_bytes': int(ZTZ.numel() * 8 + ZTy.numel() * 8)}))
+            'allreduce_bytes': int(F * F * 8 + F * 8), 'solve_ms': t_solve * 1e3, 'solve_finite': solved,
+            'solver': 'Cholesky (potrf + potrs, fp64), llambda 1e-5'}))
     if dist is not None:
         dist.destroy_process_group()
 

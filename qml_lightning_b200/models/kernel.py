@@ -231,14 +231,17 @@ class BaseKernel():
         definite, so a Cholesky factorisation replaces upstream's LU; LU is the fallback if the factorisation fails."""
         ZTZ, ZtrainY = self.build_Z_components(X, Q, E, F, cells, inv_cells, print_info, cpu_solve, ntiles,
                                                use_specialized_matmul, distributed)
-        ZTZ.diagonal().add_(self.llambda)
-        rhs = ZtrainY.to(ZTZ.device)
-        L, info = torch.linalg.cholesky_ex(ZTZ)
-        if int(info) == 0:
-            alpha = torch.cholesky_solve(rhs, L)[:, 0]
-        else:
-            alpha = torch.linalg.solve(ZTZ, rhs)[:, 0]
+        alpha = self.solve_normal_equations(ZTZ, ZtrainY)
         self.alpha = alpha.to(self.rep.device)
         self.is_trained = True
         self._parameters_changed()
         del ZTZ, ZtrainY
+
+    def solve_normal_equations(self, ZTZ, ZtrainY):
+        """alpha of ``(Z^T Z + llambda I) alpha = Z^T y``; adds llambda to the diagonal of ``ZTZ`` in place."""
+        ZTZ.diagonal().add_(self.llambda)
+        rhs = ZtrainY.to(ZTZ.device)
+        L, info = torch.linalg.cholesky_ex(ZTZ)
+        if int(info) == 0:
+            return torch.cholesky_solve(rhs, L)[:, 0]
+        return torch.linalg.solve(ZTZ, rhs)[:, 0]
