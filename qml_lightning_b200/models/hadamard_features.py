@@ -81,6 +81,11 @@ class HadamardFeaturesModel(BaseKernel, torch.nn.Module):
         return cabi.sorf_train_features(x, dx, self.Dmat[:, :self.ntransforms_int].contiguous(), self.bias, g, counts, nb, A,
                                         self.sigma)
 
+    def _element_features(self, x, dx, element_idx, grouping, counts, nb, A):
+        e = element_idx
+        return cabi.sorf_train_features(x, dx, self.Dmat[e:e + 1, :self.ntransforms_int].contiguous(), self.bias[e:e + 1].contiguous(),
+                                        grouping, counts, nb, A, self.sigma)
+
     # ---- inference -----------------------------------------------------------------------------------------------
     def forward(self, X, Z, atomIDs, molIDs, atom_counts, cell=torch.empty(0, 3, 3), inv_cell=torch.empty(0, 3, 3)):
         assert X.is_cuda, "X tensor must reside on GPU"

@@ -170,6 +170,52 @@ class BaseKernel():
         """``(Z f64[zbatch,F], G f64[zbatch,A,3,F] | None)`` for one formatted batch; implemented by the models."""
         raise NotImplementedError("Abstract method only.")
 
+    def _element_features(self, x, dx, element_idx, grouping, counts, nb, A):
+        """``(Z, G)`` of the rows of one element through the model's training kernels; implemented by the models."""
+        raise NotImplementedError("Abstract method only.")
+
+    def calculate_features(self, rep, element, indexes, feature_matrix, grad=None, derivative_matrix=None):
+        """Upstream's per-element training step (hadamard_features.py:66-80, random_features.py:60-67), kept for callers
+        that drive the element loop themselves: ``rep f32[n_e, npcas]`` are the projected rows of the atoms of
+        ``element``, ``indexes[n_e]`` their molecule numbers; adds the per-molecule features into
+        ``feature_matrix f64[nmol, F]`` and, given ``grad f32[n_e, A, 3, npcas]``, the force features (-dZ/dr) into
+        ``derivative_matrix f64[nmol, A, 3, F]``.  ``training_rows`` does the same for all elements of a batch at once."""
+        from .. import cabi
+        dev = rep.device
+        n, nb = rep.shape[0], feature_matrix.shape[0]
+        if n == 0:
+            return
+        with_grad = grad is not None and derivative_matrix is not None
+        idx = indexes.to(dev).long()
+        # position of every row among the rows of its molecule -> a private (molecule, position) slot
+        order = torch.argsort(idx, stable=True)
+        cnt = torch.bincount(idx, minlength=nb)
+        first = torch.cumsum(cnt, 0) - cnt
+        rank = torch.empty_like(idx)
+        rank[order] = torch.arange(n, device=dev) - first[idx[order]]
+        A = int(grad.shape[1]) if with_grad else int(cnt.max())
+        if int(cnt.max()) > A:
+            raise RuntimeError("calculate_features: more rows of one molecule than atoms in grad")
+        rows_cap = (n + cabi.ROW_TILE - 1) // cabi.ROW_TILE * cabi.ROW_TILE
+        slot = (idx * A + rank).to(torch.int32)
+        slot_of_row = torch.full((rows_cap,), -1, dtype=torch.int32, device=dev)
+        slot_of_row[:n] = slot
+        row_of_slot = torch.full((nb * A,), -1, dtype=torch.int32, device=dev)
+        row_of_slot[slot.long()] = torch.arange(n, dtype=torch.int32, device=dev)
+        group_start = torch.tensor([0, n], dtype=torch.int32, device=dev)
+        g = cabi.Grouping(row_of_slot, slot_of_row, group_start, rows_cap, 1)
+        x = torch.zeros(rows_cap, rep.shape[1], dtype=torch.float32, device=dev)
+        x[:n] = rep
+        dx = None
+        if with_grad:
+            dx = torch.zeros(rows_cap, A, 3, rep.shape[1], dtype=torch.float32, device=dev)
+            dx[:n] = grad
+        counts = torch.full((nb,), A, dtype=torch.int32, device=dev)
+        Z, G = self._element_features(x, dx, int(self.element2index[int(element)]), g, counts, nb, A)
+        feature_matrix += Z
+        if with_grad:
+            derivative_matrix += G
+
     @staticmethod
     def allreduce_normal_equations(ZTZ, ZtrainY):
         """Sum the per-rank partial normal equations in place (no-op without an initialised process group)."""

@@ -62,6 +62,10 @@ class RandomFourrierFeaturesModel(BaseKernel, torch.nn.Module):
         x = cabi.pca_project(rep_rows, self.reductors, g)
         return cabi.rff_train_features(x, dx, self.W, self.b, g, counts, nb, A)
 
+    def _element_features(self, x, dx, element_idx, grouping, counts, nb, A):
+        e = element_idx
+        return cabi.rff_train_features(x, dx, self.W[e:e + 1].contiguous(), self.b[e:e + 1].contiguous(), grouping, counts, nb, A)
+
     def _parameters_changed(self):
         """Rebuild the packed image of (W, b, alpha) that the tensor-core feature kernel reads; call after changing any
         of them by hand."""
