@@ -62,13 +62,33 @@ __device__ __forceinline__ void butterfly(float &a, float &b) {
     b = t - b;
 }
 
+#ifdef SORF_PACKED2
+// Two butterflies at once on the packed fp32x2 pipe of sm_100 (add.f32x2 / fma.f32x2): (a0,a1) and (b0,b1) are adjacent
+// register pairs, which holds for every stage except the one that pairs neighbouring registers.
+__device__ __forceinline__ void butterfly2(float &a0, float &a1, float &b0, float &b1) {
+    const float2 a = make_float2(a0, a1), b = make_float2(b0, b1);
+    const float2 s = __fadd2_rn(a, b);
+    const float2 d = __ffma2_rn(b, make_float2(-1.0f, -1.0f), a);  // a - b, rounded once like a subtraction
+    a0 = s.x; a1 = s.y; b0 = d.x; b1 = d.y;
+}
+#endif
+
 template <int BITS>
 __device__ __forceinline__ void fwht_regs(float (&u)[16]) {
 #pragma unroll
-    for (int h = 1; h < (1 << BITS); h <<= 1)
+    for (int h = 1; h < (1 << BITS); h <<= 1) {
+#ifdef SORF_PACKED2
+        if (h >= 2) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 2)
+                if ((i & h) == 0) butterfly2(u[i], u[i + 1], u[i | h], u[(i | h) + 1]);
+            continue;
+        }
+#endif
 #pragma unroll
         for (int i = 0; i < 16; ++i)
             if ((i & h) == 0) butterfly(u[i], u[i | h]);
+    }
 }
 
 template <int LOG2N>
@@ -288,9 +308,18 @@ sorf_energy_grad_kernel(const float *__restrict__ x, const int *__restrict__ gro
             // single transform: the sign diagonal stays in registers for the way back
             load16<C::L>(c, Ds);
 #pragma unroll
-            for (int a = 0; a < ATOMS; ++a)
+            for (int a = 0; a < ATOMS; ++a) {
+#ifdef SORF_PACKED2
+#pragma unroll
+                for (int e = 0; e < 16; e += 2) {
+                    const float2 t = __fmul2_rn(make_float2(xr[a][e], xr[a][e + 1]), make_float2(c[e], c[e + 1]));
+                    u[a][e] = t.x; u[a][e + 1] = t.y;
+                }
+#else
 #pragma unroll
                 for (int e = 0; e < 16; ++e) u[a][e] = xr[a][e] * c[e];
+#endif
+            }
             fwht_flip_n<LOG2N, ATOMS>(u, slab, l, lane, true);
             in_a = false;
         } else {
@@ -332,9 +361,19 @@ sorf_energy_grad_kernel(const float *__restrict__ x, const int *__restrict__ gro
         if (TT == 1) {
             fwht_flip_n<LOG2N, ATOMS>(u, slab, l, lane, false);
 #pragma unroll
-            for (int a = 0; a < ATOMS; ++a)
+            for (int a = 0; a < ATOMS; ++a) {
+#ifdef SORF_PACKED2
+#pragma unroll
+                for (int e = 0; e < 16; e += 2) {
+                    const float2 t = __ffma2_rn(make_float2(u[a][e], u[a][e + 1]), make_float2(c[e], c[e + 1]),
+                                                make_float2(gx[a][e], gx[a][e + 1]));
+                    gx[a][e] = t.x; gx[a][e + 1] = t.y;
+                }
+#else
 #pragma unroll
                 for (int e = 0; e < 16; ++e) gx[a][e] = fmaf(u[a][e], c[e], gx[a][e]);
+#endif
+            }
         } else {
             for (int m = T - 1; m >= 0; --m) {
                 fwht_flip_n<LOG2N, ATOMS>(u, slab, l, lane, in_a);
