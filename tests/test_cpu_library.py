@@ -88,6 +88,23 @@ def test_golden_vectors_match_oracle():
         assert np.allclose(F.numpy(), g[f'{name}_F'], rtol=1e-9, atol=1e-11)
 
 
+def test_rff_golden_vectors_match_oracle():
+    from oracle import energy_and_forces, training_rows
+    from tests import helpers as H
+    g = np.load(os.path.join(ROOT, 'tests', 'golden', 'rff_small.npz'))
+    X, Z, c = (torch.from_numpy(g[f'c0_{k}']) for k in ('X', 'Z', 'counts'))
+    species = g['c0_species'].tolist()
+    p = H.fchl_params(species)
+    model = dict(kind='rff', elements=species, reductors=torch.from_numpy(g['c0_reductors']), W=torch.from_numpy(g['c0_W']),
+                 b=torch.from_numpy(g['c0_b']), alpha=torch.from_numpy(g['c0_alpha']))
+    E, F = energy_and_forces(X, Z, c, p, model)
+    Zr, Gr = training_rows(X, Z, c, p, model)
+    assert np.allclose(E.numpy(), g['c0_E'], rtol=1e-10, atol=1e-12)
+    assert np.allclose(F.numpy(), g['c0_F'], rtol=1e-9, atol=1e-11)
+    assert np.allclose(Zr.numpy(), g['c0_Zrows'], rtol=1e-10, atol=1e-12)
+    assert np.allclose(Gr.numpy(), g['c0_Grows'], rtol=1e-9, atol=1e-11)
+
+
 def test_oracle_forces_match_finite_differences():
     from oracle import energy_and_forces
     from tests import helpers as H

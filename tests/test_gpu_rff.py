@@ -167,3 +167,34 @@ def test_rff_tc_operand_scaling(xscale, ascale):
             continue
         assert float((e1[r0:r1].double() - e_ref)[lv].abs().max()) <= 5e-6 * float(e_ref[lv].abs().max())
         assert float((g1[r0:r1].double() - g_ref)[lv].abs().max()) <= 1e-5 * float(g_ref[lv].abs().max())
+
+
+def test_rff_golden_vectors_on_gpu():
+    """CUDA RFF path (tensor-core prediction, float64 training rows) against the committed oracle vectors
+    (tests/golden/make_golden.py)."""
+    import os
+    import qml_lightning_b200 as q
+    from qml_lightning_b200 import cabi
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), 'golden', 'rff_small.npz'))
+    X, Z, c = (torch.from_numpy(g[f'c0_{k}']) for k in ('X', 'Z', 'counts'))
+    species = g['c0_species'].tolist()
+    p = H.fchl_params(species)
+    kp = H.kernel_params(p, DEV)
+    W, b, alpha, red = (torch.from_numpy(g[f'c0_{k}']).to(DEV) for k in ('W', 'b', 'alpha', 'reductors'))
+    el = torch.tensor(species, dtype=torch.float32, device=DEV)
+    E, gX = cabi.rff_predict_packed(X.to(DEV), Z.to(DEV), c.to(DEV), kp, el, red, cabi.rff_pack(W, b, alpha))
+    E_ref = torch.from_numpy(g['c0_E'])
+    assert ((E.cpu().double() - E_ref).abs() <= H.energy_tolerance(E_ref)).all()
+    assert np.abs(-gX.cpu().double().numpy() - g['c0_F']).max() <= 1e-4
+    rep = q.FCHLCuda(species=np.array(species), rcut=p.rcut, nRs2=p.nRs2, nRs3=p.nRs3, eta2=p.eta2, eta3=p.eta3,
+                     two_body_decay=p.two_body_decay, three_body_weight=p.three_body_weight,
+                     three_body_decay=p.three_body_decay, device=DEV)
+    m = q.RandomFourrierFeaturesModel(rep=rep, elements=np.array(species), sigma=2.0, nstacks=int(g['c0_nfeatures']) // int(g['c0_npcas']),
+                                      npcas=int(g['c0_npcas']))
+    m.reductors, m.W, m.b = red, W, b
+    counts = c.tolist()
+    data = m.format_data([X[i, :counts[i]].numpy() for i in range(len(counts))], [Z[i, :counts[i]].numpy() for i in range(len(counts))])
+    Zt, Gt = m.training_rows(data, with_forces=True)
+    A = data['charges'].shape[1]
+    assert np.abs(Zt.cpu().numpy() - g['c0_Zrows']).max() <= 2e-6
+    assert np.abs(Gt.cpu().numpy() - g['c0_Grows'][:, :A]).max() <= 2e-5 * max(1.0, float(np.abs(g['c0_Grows']).max()))
