@@ -18,9 +18,10 @@
 //     issued by a producer thread into a ring of three stages, and used twice;
 //   * first product, per chunk: x_hi [W_hi | W_lo] as npcas/16 MMAs with N = 64 (the lo image continues the hi image at
 //     the feature-block stride, so one descriptor covers both) and x_lo W_hi as npcas/16 MMAs with N = 32, into one of
-//     two 64-column tensor-memory buffers [hi*hi | cross terms].  Issuing an MMA costs tens of cycles whatever its size,
-//     which is more than an N = 32 MMA computes for, so the MMA count is what matters here, and two warps issue: one
-//     the even chunks, one the odd chunks;
+//     two 64-column tensor-memory buffers [hi*hi | cross terms].  Measured: an MMA occupies the tensor pipe for
+//     max(its math time, its shared-memory operand bytes / ~64 B per cycle), operands in tensor memory being free, so a
+//     small-N MMA with A in shared memory costs 80 cycles for 16 cycles of math; that is why x_hi sits in tensor memory,
+//     why the two weight images are multiplied in one instruction, and why two warps issue (even / odd chunks);
 //   * eight warps (warps w and w+4 share the rows of a tensor-memory lane quarter and take 16 features each) read the
 //     arg chunk, evaluate sin/cos, add the energy (compensated sum) and write G = -a sin(arg) (hi, lo) to shared memory
 //     as the A operand of the second product;
@@ -56,13 +57,12 @@ constexpr int NSTAGES = 3;         // weight chunks in flight
 #ifndef QMLB_RFF_FLUSH_CHUNKS
 #define QMLB_RFF_FLUSH_CHUNKS 16
 #endif
-constexpr int FLUSH_CHUNKS = QMLB_RFF_FLUSH_CHUNKS;  // gradient accumulator folded into global memory every this many chunks (even)
+constexpr int FLUSH_CHUNKS = QMLB_RFF_FLUSH_CHUNKS;  // gradient accumulator folded into global memory every this many chunks
 constexpr int WAIT_LIMIT = 1 << 22;
 constexpr size_t HEADER_BYTES = 256;
 constexpr int EXP_CLAMP = 40;
 
 static_assert(BM == QMLB_ROW_TILE, "a block must cover exactly one row tile");
-static_assert(FLUSH_CHUNKS % 2 == 0, "flush groups must hold whole chunk pairs");
 
 struct PackHeader {
     unsigned max_w_bits;   // bit pattern of max |W|
@@ -126,8 +126,7 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void *src, uint32_
 }
 // A shared-memory descriptor is kept as two 32-bit words so that stepping through an operand is one 32-bit add on the
 // low word (start address >> 4 in bits 0-13, leading byte offset >> 4 in bits 16-29); the high word (stride byte
-// offset >> 4, descriptor version 1 at bit 14, no swizzle) never changes.  The thread that issues the MMAs is
-// instruction bound, so the wrappers keep the per-MMA instruction count minimal.
+// offset >> 4, descriptor version 1 at bit 14, no swizzle) never changes.
 __device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) { return ((saddr >> 4) & 0x3FFFu) | ((lbo_bytes >> 4) << 16); }
 __device__ __forceinline__ uint32_t desc_hi(uint32_t sbo_bytes) { return (sbo_bytes >> 4) | (1u << 14); }
 
@@ -499,12 +498,10 @@ rff_tc_kernel(const float *__restrict__ x, const int *__restrict__ group_start, 
         if (h == 0 && ok) atom_energy[row0 + r] = live ? eacc + energy_half[r] : 0.f;
     } else if (warp == MMA_WARP || warp == MMA_WARP + 3) {
         // ------------------------------------------------------------------ MMAs of the first product: arg = x W
-        // Issuing an MMA costs a thread several tens of cycles whatever the MMA's size, and an N = 32 MMA computes for 16,
-        // so (a) the count is kept low: x_hi multiplies [W_hi | W_lo] in one N = 2 FC instruction (the lo image follows
-        // the hi image at the feature-block stride) and x_lo multiplies W_hi with N = FC into the cross-term columns;
-        // (b) two warps issue, one the even chunks (arg buffer 0), one the odd chunks (arg buffer 1); (c) the whole warp
-        // runs the loop in uniform control flow and only the MMA and commit instructions are left to lane 0, so that
-        // descriptors and addresses are warp-uniform values.
+        // x_hi multiplies [W_hi | W_lo] in one N = 2 FC instruction (the lo image follows the hi image at the feature-block
+        // stride) and x_lo multiplies W_hi with N = FC into the cross-term columns; two warps issue, one the even chunks
+        // (arg buffer 0), one the odd chunks (arg buffer 1); the whole warp runs the loop in uniform control flow and only
+        // the MMA and commit instructions are left to lane 0.
         // D = F32, A = B = F16, A K-major, B MN-major (N = features)
         constexpr uint32_t idesc_wide = (1u << 4) | (1u << 16) | ((uint32_t)((2 * FC) >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
         constexpr uint32_t idesc_one = (1u << 4) | (1u << 16) | ((uint32_t)(FC >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
