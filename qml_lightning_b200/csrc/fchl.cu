@@ -337,7 +337,11 @@ fchl_forward_kernel(const float *__restrict__ X, const float *__restrict__ Z, co
 // For centre atom i with incoming gradient row g (length repsize) every term of the representation is a function
 // of the three distances of a triplet (or the one distance of a pair), so the chain rule is carried out on
 // (r_ij, r_ik, r_jk) and mapped to the three atoms along the unit vectors.
-__global__ void __launch_bounds__(FCHL_THREADS)
+// The kernel is latency bound (dependent shared-memory loads and exp2 in the per-triplet loops), so it is compiled for
+// 8 resident blocks per SM (64 registers, one 4-byte spill) and the radial loop is unrolled twice: 2.05 -> 1.66 ms on
+// 10,000 21-atom molecules; 5 / 6 / 7 blocks gave 1.87 / 1.82 / 1.75 ms.
+constexpr int BWD_UNROLL = 2;
+__global__ void __launch_bounds__(FCHL_THREADS, 8)
 fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, const int *__restrict__ counts,
                      const float *__restrict__ species, const float *__restrict__ Rs2, const float *__restrict__ Rs3,
                      const float *__restrict__ cell, const float *__restrict__ icell, FchlK K,
@@ -420,6 +424,7 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
                 float Gc = 0.f, Gs = 0.f, Gr = 0.f;
                 if (pair_ok) {
                     const float2 *gb2 = reinterpret_cast<const float2 *>(gb);
+#pragma unroll BWD_UNROLL
                     for (int l = 0; l < K.nRs3; ++l) {
                         const float d = rbar - sRs3[l];
                         const float radial = exp2f(c_exp * d * d);
