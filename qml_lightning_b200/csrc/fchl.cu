@@ -341,7 +341,7 @@ fchl_forward_kernel(const float *__restrict__ X, const float *__restrict__ Z, co
 // 8 resident blocks per SM (64 registers, one 4-byte spill) and the radial loop is unrolled twice: 2.05 -> 1.66 ms on
 // 10,000 21-atom molecules; 5 / 6 / 7 blocks gave 1.87 / 1.82 / 1.75 ms.
 constexpr int BWD_UNROLL = 2;
-__global__ void __launch_bounds__(FCHL_THREADS, 8)
+__global__ void __launch_bounds__(FCHL_THREADS, 32 / FCHL_WARPS)
 fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, const int *__restrict__ counts,
                      const float *__restrict__ species, const float *__restrict__ Rs2, const float *__restrict__ Rs3,
                      const float *__restrict__ cell, const float *__restrict__ icell, FchlK K,
