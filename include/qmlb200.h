@@ -164,6 +164,17 @@ int qmlb_pca_project_tc(const float *in, const float *reductors, const int *grou
                         int sub_rows, int repsize, int npcas, int transpose, float *out, qmlb_stream_t stream);
 int qmlb_tc_timeouts(void);
 
+/* The same projection with the projection matrices split (hi + lo TF32) and tiled once per call into the shared-memory
+ * image of every (element, column tile, 32-k chunk), so that the kernel fetches its B operand with bulk copies and a
+ * block covers up to 256 output columns (dimensionality_reduction.py:47-58 and its autograd transpose).  This is what
+ * qmlb_sorf_predict / qmlb_rff_predict_packed use.  Usage: qmlb_pca_pack_bytes -> buffer (128-byte aligned) ->
+ * qmlb_pca_pack (one direction per buffer: transpose = 0 projection, 1 transposed product) -> qmlb_pca_project_packed. */
+size_t qmlb_pca_pack_bytes(int nelements, int repsize, int npcas, int transpose);
+int qmlb_pca_pack(const float *reductors, int nelements, int repsize, int npcas, int transpose, void *packed,
+                  size_t packed_bytes, qmlb_stream_t stream);
+int qmlb_pca_project_packed(const float *in, const void *packed, const int *group_start, int nelements, size_t rows_cap,
+                            int repsize, int npcas, int transpose, float *out, qmlb_stream_t stream);
+
 /* ---- SORF ----------------------------------------------------------------------------------- */
 
 /* hadamard_kernel / hadamard_gpu (cuda/hadamard_kernel.cu:5-102, 719-737), hadamard_transform_gpu

@@ -39,6 +39,9 @@ SIGNATURES = {
     'qmlb_pca_project': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_int, c_int, c_int, c_void_p, c_void_p]),
     'qmlb_pca_project_tc': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     'qmlb_tc_timeouts': (c_int, []),
+    'qmlb_pca_pack_bytes': (c_size_t, [c_int, c_int, c_int, c_int]),
+    'qmlb_pca_pack': (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    'qmlb_pca_project_packed': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_int, c_int, c_int, c_void_p, c_void_p]),
     'qmlb_sorf_coefficients': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]),
     'qmlb_sorf_coefficients_backward': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]),
     'qmlb_cos_features': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),

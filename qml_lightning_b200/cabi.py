@@ -416,6 +416,22 @@ def rff_predict_packed(X, Z, atom_counts, fchl, elements, reductors, packed, cel
     return energy, grad_X
 
 
+def pca_project_packed(inp, reductors, grouping, transpose=False, out=None):
+    """:func:`pca_project` through ``qmlb_pca_pack`` + ``qmlb_pca_project_packed`` (pre-split B operand, bulk copies)."""
+    nel, repsize, npcas = reductors.shape
+    lib = _lib.load()
+    nbytes = lib.qmlb_pca_pack_bytes(nel, repsize, npcas, int(bool(transpose)))
+    packed = torch.empty(nbytes, dtype=torch.uint8, device=inp.device)
+    check(lib.qmlb_pca_pack(_p(reductors.contiguous(), torch.float32, 'reductors'), nel, repsize, npcas, int(bool(transpose)),
+                            _p(packed), nbytes, _stream(inp.device)), 'qmlb_pca_pack')
+    rows = grouping.rows_cap
+    if out is None:
+        out = torch.empty(rows, repsize if transpose else npcas, dtype=torch.float32, device=inp.device)
+    check(lib.qmlb_pca_project_packed(_p(inp, torch.float32, 'in'), _p(packed), _p(grouping.group_start), nel, rows, repsize, npcas,
+                                      int(bool(transpose)), _p(out), _stream(inp.device)), 'qmlb_pca_project_packed')
+    return out
+
+
 def pca_project_jacobian(jac_rows, reductors, grouping):
     """``[rows, A, 3, repsize] -> [rows, A, 3, npcas]`` on element-grouped rows."""
     nel, repsize, npcas = reductors.shape

@@ -300,14 +300,15 @@ pca_tc_kernel(const float *__restrict__ in, const float *__restrict__ P, const i
 }  // namespace
 
 namespace qmlb {
-int rff_tc_timeouts();  // rff_tc.cu
+int rff_tc_timeouts();   // rff_tc.cu
+int pca_tc2_timeouts();  // pca_tc2.cu
 }
 
 extern "C" int qmlb_tc_timeouts(void) {
     int v = -1;
     if (cudaMemcpyFromSymbol(&v, g_tc_timeouts, sizeof(int)) != cudaSuccess) return -1;
-    const int w = qmlb::rff_tc_timeouts();
-    return w < 0 ? -1 : v + w;
+    const int w = qmlb::rff_tc_timeouts(), u = qmlb::pca_tc2_timeouts();
+    return (w < 0 || u < 0) ? -1 : v + w + u;
 }
 
 extern "C" int qmlb_pca_project_tc(const float *in, const float *reductors, const int *group_start, int nelements,

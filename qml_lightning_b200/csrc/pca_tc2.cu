@@ -1,0 +1,412 @@
+// Per-element PCA projection on the tensor cores with a pre-split, pre-tiled B operand.
+//
+//   out[r, n] = sum_k in[r, k] * B_e[n, k],   B_e[n,k] = P_e[k,n] (projection) or P_e[n,k] (its transpose)
+//
+// Same arithmetic as pca_tc.cu (tcgen05.mma kind::tf32, every fp32 operand split into hi + lo TF32 parts, products
+// hi*hi + hi*lo + lo*hi accumulated in fp32), reorganised around what limited that kernel: every block re-split its
+// B tile (the same projection matrix for all row tiles of an element) and a 128-column tile meant reading and
+// splitting the A rows once per column tile.  Here
+//   * qmlb_pca_pack splits the projection matrices once per call into the exact shared-memory image of every
+//     (element, column tile, 32-k chunk): hi image then lo image, canonical K-major no-swizzle core matrices
+//     [8 n][4 k]; the main kernel fetches a chunk with one cp.async.bulk;
+//   * a block owns 128 rows x up to 256 columns, so A is read and split once (twice for outputs wider than 256);
+//   * eight worker warps stage the A chunks (one row half-chunk per thread) and drain the accumulators, one warp
+//     issues the MMAs, one warp issues the copies; two stages of (A 32 KB + B up to 64 KB).
+// The tensor core adds into its fp32 accumulator with truncation towards zero, which biases long accumulations.  The
+// small cross terms (hi*lo, lo*hi) therefore have their own accumulator columns, and the accumulators are folded into
+// fp32 registers every `group_chunks` chunks (3 = 96 k = 12 truncating adds of hi*hi terms for the projection, whose
+// result feeds cos(); 8 for the transposed product, K = npcas <= 256, which feeds only the force chain rule).  Folding
+// every chunk into a second accumulator buffer instead (so that it overlaps the next MMAs) was slower: the eight
+// worker warps then fold four times as often and become the bottleneck (c1 projection 0.42 ms against 0.35 ms).
+// Tensor memory: hi*hi columns [0, NT), cross-term columns [256, 256 + NT); all 512 columns are allocated.
+// Every wait is bounded; a block that times out skips its stores, waits (bounded) for copies and MMAs in flight,
+// frees its tensor memory and counts the event (qmlb_tc_timeouts).
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;          // rows per block = QMLB_ROW_TILE
+constexpr int BK = 32;           // k per chunk (4 MMA steps of 8)
+constexpr int NT_MAX = 256;      // columns per block
+constexpr int WORKER_WARPS = 8;  // warps 0-7: A staging + accumulator drain (warps w and w+4 share a tensor-memory lane quarter)
+constexpr int MMA_WARP = 8;      // warp 8: MMA issue (+ tensor-memory allocation), warp 9: B copies
+constexpr int NTHREADS = 320;
+constexpr int NSTAGES = 2;
+constexpr int WAIT_LIMIT = 1 << 22;
+constexpr uint32_t TMEM_COLS = 512, COL_MAIN = 0, COL_CROSS = 256;
+constexpr uint32_t A_HALF = BM * BK * 4;           // A hi (or lo) image of one chunk: 16 KB
+static_assert(BM == QMLB_ROW_TILE, "a block must cover exactly one row tile");
+
+__device__ int g_pca_tc2_timeouts = 0;
+
+struct Tiling {
+    int K, Nout, ntiles, NT, nchunks;
+    size_t chunk_bytes;          // 2 images of NT x BK floats
+};
+
+__host__ __device__ inline Tiling make_tiling(int repsize, int npcas, int transpose) {
+    Tiling t;
+    t.K = transpose ? npcas : repsize;
+    t.Nout = transpose ? repsize : npcas;
+    t.ntiles = (t.Nout + NT_MAX - 1) / NT_MAX;
+    t.NT = ((t.Nout + t.ntiles - 1) / t.ntiles + 15) / 16 * 16;
+    t.nchunks = (t.K + BK - 1) / BK;
+    t.chunk_bytes = (size_t)2 * t.NT * BK * 4;
+    return t;
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded parity wait; false on time-out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (int it = 0; it < WAIT_LIMIT; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+// Shared-memory descriptor as two 32-bit words: low = start address >> 4 | (leading byte offset >> 4) << 16, high =
+// stride byte offset >> 4 | descriptor version 1 (bit 14 of the high word); no swizzle.
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) { return ((saddr >> 4) & 0x3FFFu) | ((lbo_bytes >> 4) << 16); }
+__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint32_t alo, uint32_t ahi, uint32_t blo, uint32_t bhi, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n\t}"
+        :
+        : "r"(tmem_d), "r"(alo), "r"(ahi), "r"(blo), "r"(bhi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void split_tf32(float x, float &hi, float &lo) {
+    uint32_t h;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+    hi = __uint_as_float(h);
+    const float r = x - hi;  // exact in fp32
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(r));  // round (the tensor core would truncate)
+    lo = __uint_as_float(h);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// packing: one thread per (element, tile, chunk, column n, group of 4 k) -> 16 bytes of hi and of lo
+// ---------------------------------------------------------------------------------------------------------------
+__global__ void pca_pack_kernel(const float *__restrict__ P, int nel, int repsize, int npcas, int transpose, Tiling t,
+                                unsigned char *__restrict__ packed) {
+    const size_t per_chunk = (size_t)t.NT * (BK / 4);
+    const size_t total = (size_t)nel * t.ntiles * t.nchunks * per_chunk;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int n_in = (int)(i % t.NT);                   // consecutive threads: consecutive columns
+        const int kq = (int)((i / t.NT) % (BK / 4));
+        const size_t blob = i / per_chunk;
+        const int c = (int)(blob % t.nchunks);
+        const int tile = (int)((blob / t.nchunks) % t.ntiles);
+        const int e = (int)(blob / ((size_t)t.nchunks * t.ntiles));
+        const int n = tile * t.NT + n_in;
+        const float *Pe = P + (size_t)e * repsize * npcas;
+        float hi[4], lo[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int k = c * BK + kq * 4 + q;
+            float v = 0.f;
+            if (n < t.Nout && k < t.K) v = transpose ? Pe[(size_t)n * npcas + k] : Pe[(size_t)k * npcas + n];
+            split_tf32(v, hi[q], lo[q]);
+        }
+        unsigned char *dst = packed + blob * t.chunk_bytes + ((size_t)(kq * (t.NT / 8) + (n_in >> 3)) * 128) + (size_t)(n_in & 7) * 16;
+        *reinterpret_cast<float4 *>(dst) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<float4 *>(dst + t.chunk_bytes / 2) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// main kernel
+// ---------------------------------------------------------------------------------------------------------------
+enum { A_FULL = 0, B_FULL = A_FULL + NSTAGES, STAGE_FREE = B_FULL + NSTAGES, ACC_FULL = STAGE_FREE + NSTAGES, ACC_FREE, ALL_DONE, NBARS };
+
+// 10 warps = 3 per SM sub-partition at most, whose 16,384 registers allow 168 per thread; the register row of the drain
+// (128 floats, touched once per group) is what spills.
+__global__ void __launch_bounds__(NTHREADS, 1)
+pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ packed, const int *__restrict__ group_start, int nel,
+               Tiling t, int group_chunks, float *__restrict__ out) {
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ __align__(8) uint64_t bars[NBARS];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int failed;
+
+    const int row0 = blockIdx.x * BM;
+    const int tile = blockIdx.y;
+    if (row0 >= group_start[nel]) return;
+    int e = 0;
+    while (e + 1 < nel && row0 >= group_start[e + 1]) ++e;
+    const unsigned char *blobs = packed + ((size_t)e * t.ntiles + tile) * t.nchunks * t.chunk_bytes;
+    const int K = t.K, NT = t.NT, nchunks = t.nchunks;
+    const uint32_t b_half = (uint32_t)(t.chunk_bytes / 2), stage_bytes = 2 * A_HALF + (uint32_t)t.chunk_bytes;
+
+    const uint32_t sbase = (smem_u32(smem_dyn) + 127u) & ~127u;
+    unsigned char *sptr = smem_dyn + (sbase - smem_u32(smem_dyn));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    auto bar = [&](int i) { return smem_u32(&bars[i]); };
+
+    if (tid == 0) {
+        for (int s = 0; s < NSTAGES; ++s) {
+            mbar_init(bar(A_FULL + s), WORKER_WARPS); mbar_init(bar(B_FULL + s), 1); mbar_init(bar(STAGE_FREE + s), 1);
+        }
+        mbar_init(bar(ACC_FULL), 1); mbar_init(bar(ACC_FREE), WORKER_WARPS); mbar_init(bar(ALL_DONE), 1);
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before();
+    __syncthreads();
+    fence_after();
+    // all 512 columns are allocated, so the allocation starts at column 0 (checked) and addresses are constants
+    const uint32_t tmem_alloc = tmem_slot;
+    constexpr uint32_t tmem = 0u;
+    const bool tmem_ok = tmem_alloc == 0u;
+    const int ngroups = (nchunks + group_chunks - 1) / group_chunks;
+
+    if (warp < WORKER_WARPS) {
+        // ------------------------------------------------------------------ A staging + accumulator drain
+        // thread = (row r, half h): k sub-range [16 h, 16 h + 16) of every chunk; columns [h NT/2, (h+1) NT/2) of the tile
+        const int r = (warp & 3) * 32 + lane, h = warp >> 2;
+        const uint32_t lane_field = (uint32_t)((warp & 3) * 32) << 16;
+        const int half = NT / 2;
+        const float *src = in + (size_t)(row0 + r) * K;
+        const bool vec = (K & 3) == 0;
+        float racc[NT_MAX / 2];
+#pragma unroll
+        for (int i = 0; i < NT_MAX / 2; ++i) racc[i] = 0.f;
+        float4 pre[4];
+        auto fetch = [&](int c) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int k = c * BK + h * 16 + q * 4;
+                if (vec && k + 3 < K) pre[q] = *reinterpret_cast<const float4 *>(src + k);
+                else {
+                    float v[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) v[i] = (k + i < K) ? src[k + i] : 0.f;
+                    pre[q] = make_float4(v[0], v[1], v[2], v[3]);
+                }
+            }
+        };
+        // fold the accumulators of group g into the register row
+        auto drain = [&](int g) {
+            if (!mbar_wait(bar(ACC_FULL), (uint32_t)g & 1u)) return false;
+            fence_after();
+            const uint32_t base = tmem + lane_field + (uint32_t)(h * half);
+#pragma unroll
+            for (int cc = 0; cc < NT_MAX / 2; cc += 8) {
+                if (cc < half) {
+                    uint32_t m[8], x[8];
+                    tmem_ld8(base + COL_MAIN + (uint32_t)cc, m);
+                    tmem_ld8(base + COL_CROSS + (uint32_t)cc, x);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) racc[cc + i] += __uint_as_float(m[i]) + __uint_as_float(x[i]);
+                }
+            }
+            fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(ACC_FREE));
+            return true;
+        };
+        bool ok = tmem_ok;
+        if (ok) fetch(0);
+        for (int c = 0; c < nchunks && ok; ++c) {
+            const int s = c % NSTAGES;
+            // the MMAs that read this stage two chunks ago must have completed
+            if (c >= NSTAGES && !mbar_wait(bar(STAGE_FREE + s), (uint32_t)((c / NSTAGES) - 1) & 1u)) { ok = false; break; }
+            unsigned char *a_hi = sptr + (size_t)s * stage_bytes, *a_lo = a_hi + A_HALF;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float v[4] = {pre[q].x, pre[q].y, pre[q].z, pre[q].w};
+                float hi[4], lo[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) split_tf32(v[i], hi[i], lo[i]);
+                // canonical K-major image: 8 rows x 4 k per 128-byte core matrix, k blocks outermost
+                const uint32_t off = (uint32_t)((h * 4 + q) * 16 + (r >> 3)) * 128u + (uint32_t)(r & 7) * 16u;
+                *reinterpret_cast<float4 *>(a_hi + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<float4 *>(a_lo + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+            }
+            if (c + 1 < nchunks) fetch(c + 1);
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(A_FULL + s));
+
+            // the group that ended with the previous chunk is folded now, after this chunk has been staged, so that the
+            // staging overlaps the group's last MMAs
+            if (c >= 1 && ((c - 1) % group_chunks) == group_chunks - 1) ok = drain((c - 1) / group_chunks);
+        }
+        if (ok) ok = drain((nchunks - 1) / group_chunks);
+        if (ok) {
+            float *dst = out + (size_t)(row0 + r) * t.Nout + (size_t)tile * NT + h * half;
+            const int col0 = tile * NT + h * half;
+            const bool vec_out = (t.Nout & 3) == 0 && (half & 3) == 0;
+#pragma unroll
+            for (int cc = 0; cc < NT_MAX / 2; cc += 4) {
+                if (cc < half) {
+                    if (vec_out && col0 + cc + 3 < t.Nout) {
+                        *reinterpret_cast<float4 *>(dst + cc) = make_float4(racc[cc], racc[cc + 1], racc[cc + 2], racc[cc + 3]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            if (cc + i < half && col0 + cc + i < t.Nout) dst[cc + i] = racc[cc + i];
+                    }
+                }
+            }
+        } else {
+            failed = 1;  // benign race: every writer stores 1
+        }
+    } else if (warp == MMA_WARP) {
+        // ------------------------------------------------------------------ MMA issue (whole warp in uniform control flow)
+        // D = F32, A = B = TF32, both K-major, N = NT, M = 128
+        const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+        constexpr uint32_t ab_hi = (128u >> 4) | (1u << 14);          // 8-row groups 128 B apart
+        const uint32_t b_lbo = (uint32_t)(NT / 8) * 128u;              // next 4-k block of B
+        bool ok = tmem_ok;
+        for (int c = 0; c < nchunks && ok; ++c) {
+            const int s = c % NSTAGES;
+            const uint32_t par = (uint32_t)(c / NSTAGES) & 1u;
+            const int g = c / group_chunks;
+            const bool first = (c % group_chunks) == 0;
+            bool w = mbar_wait(bar(A_FULL + s), par);
+            w = mbar_wait(bar(B_FULL + s), par) && w;
+            if (first && g > 0) w = mbar_wait(bar(ACC_FREE), (uint32_t)(g - 1) & 1u) && w;
+            if (!__all_sync(QMLB_FULL_MASK, w)) { ok = false; break; }
+            fence_after();
+            const uint32_t a_base = sbase + (uint32_t)s * stage_bytes, b_base = a_base + 2 * A_HALF;
+            const uint32_t ah = desc_lo(a_base, 2048u), al = desc_lo(a_base + A_HALF, 2048u);
+            const uint32_t bh = desc_lo(b_base, b_lbo), bl = desc_lo(b_base + b_half, b_lbo);
+            const uint32_t b_step = (2u * b_lbo) >> 4;                 // two 4-k blocks per MMA
+            if (lane == 0) {
+#pragma unroll
+                for (int j = 0; j < BK / 8; ++j) {
+                    const uint32_t acc = (first && j == 0) ? 0u : 1u;
+                    mma_tf32(tmem + COL_CROSS, ah + j * 256, ab_hi, bl + j * b_step, ab_hi, idesc, acc);
+                    mma_tf32(tmem + COL_CROSS, al + j * 256, ab_hi, bh + j * b_step, ab_hi, idesc, 1u);
+                    mma_tf32(tmem + COL_MAIN, ah + j * 256, ab_hi, bh + j * b_step, ab_hi, idesc, acc);
+                }
+                mma_commit(bar(STAGE_FREE + s));
+                if ((c % group_chunks) == group_chunks - 1 || c == nchunks - 1) mma_commit(bar(ACC_FULL));
+            }
+            __syncwarp();
+        }
+        // everything issued must have left the tensor pipe before the tensor memory is released
+        if (lane == 0) mma_commit(bar(ALL_DONE));
+        __syncwarp();
+        if (!mbar_wait(bar(ALL_DONE), 0u)) ok = false;
+        if (!ok) failed = 1;
+    } else {
+        // ------------------------------------------------------------------ B copies
+        if (lane == 0) {
+            bool ok = tmem_ok;
+            int issued = 0;
+            for (int c = 0; c < nchunks && ok; ++c) {
+                const int s = c % NSTAGES;
+                if (c >= NSTAGES && !mbar_wait(bar(STAGE_FREE + s), (uint32_t)((c / NSTAGES) - 1) & 1u)) { ok = false; break; }
+                mbar_expect_tx(bar(B_FULL + s), (uint32_t)t.chunk_bytes);
+                bulk_copy(sbase + (uint32_t)s * stage_bytes + 2 * A_HALF, blobs + (size_t)c * t.chunk_bytes, (uint32_t)t.chunk_bytes,
+                          bar(B_FULL + s));
+                issued = c + 1;
+            }
+            // no copy may still be in flight when the block leaves
+            for (int c = max(0, issued - NSTAGES); c < issued; ++c)
+                if (!mbar_wait(bar(B_FULL + (c % NSTAGES)), (uint32_t)(c / NSTAGES) & 1u)) ok = false;
+            if (!ok) failed = 1;
+        }
+    }
+    __syncwarp();
+    fence_before();
+    __syncthreads();
+    fence_after();
+    if (failed && tid == 0) atomicAdd(&g_pca_tc2_timeouts, 1);
+    if (warp == MMA_WARP) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_alloc), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace
+
+namespace qmlb {
+int pca_tc2_timeouts() {
+    int v = -1;
+    if (cudaMemcpyFromSymbol(&v, g_pca_tc2_timeouts, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}
+}  // namespace qmlb
+
+extern "C" size_t qmlb_pca_pack_bytes(int nelements, int repsize, int npcas, int transpose) {
+    if (nelements <= 0 || repsize <= 0 || npcas <= 0) return 0;
+    const Tiling t = make_tiling(repsize, npcas, transpose);
+    return (size_t)nelements * t.ntiles * t.nchunks * t.chunk_bytes;
+}
+
+extern "C" int qmlb_pca_pack(const float *reductors, int nelements, int repsize, int npcas, int transpose, void *packed,
+                             size_t packed_bytes, qmlb_stream_t stream) {
+    QMLB_REQUIRE(reductors && packed, "qmlb_pca_pack: null tensor");
+    QMLB_REQUIRE(nelements > 0 && repsize > 0 && npcas > 0, "qmlb_pca_pack: bad sizes");
+    QMLB_REQUIRE(packed_bytes >= qmlb_pca_pack_bytes(nelements, repsize, npcas, transpose), "qmlb_pca_pack: packed buffer too small");
+    QMLB_REQUIRE(((uintptr_t)packed & 127) == 0, "qmlb_pca_pack: packed buffer must be 128-byte aligned");
+    const Tiling t = make_tiling(repsize, npcas, transpose);
+    pca_pack_kernel<<<592, 256, 0, qmlb::as_stream(stream)>>>(reductors, nelements, repsize, npcas, transpose, t,
+                                                             static_cast<unsigned char *>(packed));
+    return qmlb::check_launch("qmlb_pca_pack");
+}
+
+extern "C" int qmlb_pca_project_packed(const float *in, const void *packed, const int *group_start, int nelements,
+                                       size_t rows_cap, int repsize, int npcas, int transpose, float *out,
+                                       qmlb_stream_t stream) {
+    QMLB_REQUIRE(in && packed && group_start && out, "qmlb_pca_project_packed: null tensor");
+    QMLB_REQUIRE(nelements > 0 && repsize > 0 && npcas > 0, "qmlb_pca_project_packed: bad sizes");
+    QMLB_REQUIRE(rows_cap % BM == 0, "qmlb_pca_project_packed: rows_cap must be a multiple of %d", BM);
+    if (rows_cap == 0) return QMLB_OK;
+    const Tiling t = make_tiling(repsize, npcas, transpose);
+    const size_t smem = (size_t)NSTAGES * (2 * A_HALF + t.chunk_bytes) + 128;
+    if (int rc = qmlb::ensure_smem(pca_tc2_kernel, smem, "qmlb_pca_project_packed")) return rc;
+    // projection: fold every 3 chunks (96 k); transposed product (K = npcas): fold once per 8 chunks
+    const int group_chunks = transpose ? 8 : 3;
+    dim3 grid((unsigned)(rows_cap / BM), (unsigned)t.ntiles);
+    pca_tc2_kernel<<<grid, NTHREADS, smem, qmlb::as_stream(stream)>>>(in, static_cast<const unsigned char *>(packed), group_start,
+                                                                      nelements, t, group_chunks, out);
+    return qmlb::check_launch("qmlb_pca_project_packed");
+}

@@ -11,7 +11,8 @@ inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 struct Workspace {
     size_t rows_cap;
-    size_t off_row_of_slot, off_slot_of_row, off_group_start, off_scratch, off_rep, off_x, off_gx, off_energy, total;
+    size_t off_row_of_slot, off_slot_of_row, off_group_start, off_scratch, off_rep, off_x, off_gx, off_energy, off_pca_fwd, off_pca_bwd, total;
+    size_t pca_fwd_bytes, pca_bwd_bytes;
     Workspace(int nb, int A, size_t n_atoms_upper, int nel, int repsize, int width) {
         const size_t slots = (size_t)nb * A;
         rows_cap = qmlb_rows_capacity(n_atoms_upper < slots ? n_atoms_upper : slots, nel);
@@ -24,6 +25,11 @@ struct Workspace {
         off_x = o;           o = align256(o + sizeof(float) * rows_cap * width);
         off_gx = o;          o = align256(o + sizeof(float) * rows_cap * width);
         off_energy = o;      o = align256(o + sizeof(float) * rows_cap);
+        // projection matrices split and tiled for the tensor-core kernel, one image per direction
+        pca_fwd_bytes = qmlb_pca_pack_bytes(nel, repsize, width, 0);
+        pca_bwd_bytes = qmlb_pca_pack_bytes(nel, repsize, width, 1);
+        off_pca_fwd = o;     o = align256(o + pca_fwd_bytes);
+        off_pca_bwd = o;     o = align256(o + pca_bwd_bytes);
         total = o;
     }
 };
@@ -62,11 +68,15 @@ int predict_pipeline(const float *X, const float *Z, const int *atom_counts, int
     if ((rc = qmlb_group_by_element(Z, atom_counts, elements, nelements, nb, A, row_of_slot, slot_of_row, group_start,
                                     W.rows_cap, base + W.off_scratch, stream))) return rc;
     if ((rc = qmlb_fchl19_forward(X, Z, atom_counts, nb, A, p, cell, inv_cell, row_of_slot, rep, stream))) return rc;
-    // both projections run on the tensor cores (tcgen05, 3xTF32 split: fp32-accurate)
-    if ((rc = qmlb_pca_project_tc(rep, reductors, group_start, nelements, W.rows_cap, 1, repsize, npcas, 0, x, stream))) return rc;
+    // both projections run on the tensor cores (tcgen05, 3xTF32 split: fp32-accurate) with the projection matrices
+    // split and tiled once per call
+    void *pca_fwd = base + W.off_pca_fwd, *pca_bwd = base + W.off_pca_bwd;
+    if ((rc = qmlb_pca_pack(reductors, nelements, repsize, npcas, 0, pca_fwd, W.pca_fwd_bytes, stream))) return rc;
+    if ((rc = qmlb_pca_pack(reductors, nelements, repsize, npcas, 1, pca_bwd, W.pca_bwd_bytes, stream))) return rc;
+    if ((rc = qmlb_pca_project_packed(rep, pca_fwd, group_start, nelements, W.rows_cap, repsize, npcas, 0, x, stream))) return rc;
     if ((rc = features(x, group_start, slot_of_row, W.rows_cap, atom_energy, gx))) return rc;
     // the representation buffer is reused for d(energy)/d(representation)
-    if ((rc = qmlb_pca_project_tc(gx, reductors, group_start, nelements, W.rows_cap, 1, repsize, npcas, 1, rep, stream))) return rc;
+    if ((rc = qmlb_pca_project_packed(gx, pca_bwd, group_start, nelements, W.rows_cap, repsize, npcas, 1, rep, stream))) return rc;
     return qmlb_fchl19_backward(X, Z, atom_counts, nb, A, p, cell, inv_cell, row_of_slot, rep, grad_X, atom_energy, energy,
                                 stream);
 }

@@ -250,3 +250,27 @@ def test_fused_sorf_energy_grad(cabi, N, T, fast):
         assert (e_atom[r0:r1][live] - e_ref.detach()[live]).abs().max() <= tol * max(1.0, float(e_ref.abs().max()))
         assert (gx[r0:r1][live] - g_ref[live]).abs().max() <= tol * max(1.0, float(g_ref.abs().max()))
         assert (e_atom[r0:r1][~live] == 0).all()
+
+
+@pytest.mark.parametrize('repsize,npcas', [(336, 256), (780, 128), (100, 32), (336, 512), (72, 16), (130, 48)])
+def test_pca_project_packed_matches_float64(repsize, npcas):
+    """The pipeline's projection kernel (pre-split projection matrices, up to 256 columns per block, bulk-copied B
+    operand) in both directions: widths that need one column tile, several (512, 780), ragged k chunks (100, 130, 72)
+    and a width that is not a multiple of 16 per tile (48 -> tile of 48, 130 -> 144)."""
+    from qml_lightning_b200 import cabi
+    X, Z, c, species = H.batch_mixed(40, seed=repsize)
+    g = cabi.group_by_element(Z.to(DEV), c.to(DEV), torch.tensor(species, dtype=torch.float32, device=DEV))
+    gen = torch.Generator().manual_seed(npcas)
+    red = torch.randn(len(species), repsize, npcas, generator=gen) / repsize ** 0.5
+    gs = g.group_start.cpu()
+    events_before = cabi.tc_timeouts()
+    for transpose in (False, True):
+        src = torch.randn(g.rows_cap, npcas if transpose else repsize, generator=gen)
+        out = cabi.pca_project_packed(src.to(DEV), red.to(DEV), g, transpose=transpose).cpu().double()
+        for ei in range(len(species)):
+            r0, r1 = int(gs[ei]), int(gs[ei + 1])
+            if r1 == r0:
+                continue
+            ref = src[r0:r1].double() @ (red[ei].double().T if transpose else red[ei].double())
+            assert (out[r0:r1] - ref).abs().max() <= 3e-6 * max(1.0, float(ref.abs().max()))
+    assert cabi.tc_timeouts() == events_before
