@@ -206,6 +206,8 @@ def run_training(args, rank, world, local):
     model.build_Z_components(Xl[:64], Zl[:64], E[:64], Fl[:64], print_info=False)     # warm-up (cuBLAS handle, allocator)
     torch.cuda.synchronize()
     if dist is not None:
+        warm = torch.ones(1 << 20, dtype=torch.float64, device=dev)
+        dist.all_reduce(warm)                      # communicator set-up stays out of the timed all-reduce
         dist.barrier()
     t0 = time.perf_counter()
     ZTZ, ZTy = model.build_Z_components(Xl, Zl, E, Fl, print_info=False)
