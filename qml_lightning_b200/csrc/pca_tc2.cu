@@ -23,6 +23,8 @@
 // frees its tensor memory and counts the event (qmlb_tc_timeouts).
 #include <math.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace {
@@ -40,6 +42,9 @@ constexpr uint32_t A_HALF = BM * BK * 4;           // A hi (or lo) image of one 
 static_assert(BM == QMLB_ROW_TILE, "a block must cover exactly one row tile");
 
 __device__ int g_pca_tc2_timeouts = 0;
+// Sequence number of the last launch in which a block gave up on a wait; the remaining blocks of that launch return at
+// once (the host passes a fresh number with every launch).
+__device__ unsigned g_pca_tc2_failed_launch = 0;
 
 struct Tiling {
     int K, Nout, ntiles, NT, nchunks;
@@ -163,7 +168,7 @@ enum { A_FULL = 0, B_FULL = A_FULL + NSTAGES, STAGE_FREE = B_FULL + NSTAGES, ACC
 // (128 floats, touched once per group) is what spills.
 __global__ void __launch_bounds__(NTHREADS, 1)
 pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ packed, const int *__restrict__ group_start, int nel,
-               Tiling t, int group_chunks, float *__restrict__ out) {
+               Tiling t, int group_chunks, float *__restrict__ out, unsigned launch_seq) {
     extern __shared__ unsigned char smem_dyn[];
     __shared__ __align__(8) uint64_t bars[NBARS];
     __shared__ uint32_t tmem_slot;
@@ -172,6 +177,7 @@ pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ p
     const int row0 = blockIdx.x * BM;
     const int tile = blockIdx.y;
     if (row0 >= group_start[nel]) return;
+    if (*reinterpret_cast<volatile unsigned *>(&g_pca_tc2_failed_launch) == launch_seq) return;
     int e = 0;
     while (e + 1 < nel && row0 >= group_start[e + 1]) ++e;
     const unsigned char *blobs = packed + ((size_t)e * t.ntiles + tile) * t.nchunks * t.chunk_bytes;
@@ -359,7 +365,10 @@ pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ p
     fence_before();
     __syncthreads();
     fence_after();
-    if (failed && tid == 0) atomicAdd(&g_pca_tc2_timeouts, 1);
+    if (failed && tid == 0) {
+        atomicAdd(&g_pca_tc2_timeouts, 1);
+        atomicExch(&g_pca_tc2_failed_launch, launch_seq);
+    }
     if (warp == MMA_WARP) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_alloc), "r"(TMEM_COLS) : "memory");
     }
@@ -406,7 +415,9 @@ extern "C" int qmlb_pca_project_packed(const float *in, const void *packed, cons
     // projection: fold every 3 chunks (96 k); transposed product (K = npcas): fold once per 8 chunks
     const int group_chunks = transpose ? 8 : 3;
     dim3 grid((unsigned)(rows_cap / BM), (unsigned)t.ntiles);
+    static std::atomic<unsigned> launches{0};
+    const unsigned seq = ++launches;   // never 0, the initial value of the device-side marker
     pca_tc2_kernel<<<grid, NTHREADS, smem, qmlb::as_stream(stream)>>>(in, static_cast<const unsigned char *>(packed), group_start,
-                                                                      nelements, t, group_chunks, out);
+                                                                      nelements, t, group_chunks, out, seq);
     return qmlb::check_launch("qmlb_pca_project_packed");
 }

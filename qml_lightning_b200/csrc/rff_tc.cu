@@ -42,6 +42,7 @@
 #include <cuda_fp16.h>
 #include <math.h>
 
+#include <atomic>
 #include <type_traits>
 
 #include "common.cuh"
@@ -71,6 +72,10 @@ struct PackHeader {
 };
 
 __device__ int g_rff_tc_timeouts = 0;
+// Sequence number of the last launch in which a block gave up on a wait: the remaining blocks of that launch return at
+// once instead of each running into the same bounded waits (a launch that cannot make progress then ends within one
+// wave of blocks).  The host passes a fresh number with every launch.
+__device__ unsigned g_rff_tc_failed_launch = 0;
 
 __host__ __device__ constexpr size_t chunk_bytes(int K) { return (size_t)2 * K * FC * 2 + 3 * FC * 4; }
 
@@ -284,7 +289,8 @@ struct Smem {
 template <int K, bool FAST>
 __global__ void __launch_bounds__(NTHREADS, 1)
 rff_tc_kernel(const float *__restrict__ x, const int *__restrict__ group_start, const int *__restrict__ slot_of_row, int nel,
-              const unsigned char *__restrict__ packed, float *__restrict__ atom_energy, float *__restrict__ grad_x) {
+              const unsigned char *__restrict__ packed, float *__restrict__ atom_energy, float *__restrict__ grad_x,
+              unsigned launch_seq) {
     using S = Smem<K>;
     constexpr int KB = K / 8;
     extern __shared__ unsigned char smem_dyn[];
@@ -296,6 +302,7 @@ rff_tc_kernel(const float *__restrict__ x, const int *__restrict__ group_start, 
 
     const int row0 = blockIdx.x * BM;
     if (row0 >= group_start[nel]) return;
+    if (*reinterpret_cast<volatile unsigned *>(&g_rff_tc_failed_launch) == launch_seq) return;
     int e = 0;
     while (e + 1 < nel && row0 >= group_start[e + 1]) ++e;
 
@@ -598,7 +605,10 @@ rff_tc_kernel(const float *__restrict__ x, const int *__restrict__ group_start, 
     fence_before();
     __syncthreads();
     fence_after();
-    if (failed && tid == 0) atomicAdd(&g_rff_tc_timeouts, 1);
+    if (failed && tid == 0) {
+        atomicAdd(&g_rff_tc_timeouts, 1);
+        atomicExch(&g_rff_tc_failed_launch, launch_seq);
+    }
     if (warp == MMA_WARP) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_alloc), "r"(TMEM_COLS) : "memory");
     }
@@ -609,12 +619,14 @@ int launch_rff_tc(const float *x, const int *group_start, const int *slot_of_row
                   const unsigned char *packed, int fast, float *atom_energy, float *grad_x, cudaStream_t st) {
     const size_t smem = Smem<K>::TOTAL + 128;
     const unsigned grid = (unsigned)(rows_cap / BM);
+    static std::atomic<unsigned> launches{0};
+    const unsigned seq = ++launches;   // never 0, the initial value of the device-side marker (wraps after 2^32 launches)
     if (fast) {
         if (int rc = qmlb::ensure_smem(rff_tc_kernel<K, true>, smem, "qmlb_rff_energy_grad_tc")) return rc;
-        rff_tc_kernel<K, true><<<grid, NTHREADS, smem, st>>>(x, group_start, slot_of_row, nel, packed, atom_energy, grad_x);
+        rff_tc_kernel<K, true><<<grid, NTHREADS, smem, st>>>(x, group_start, slot_of_row, nel, packed, atom_energy, grad_x, seq);
     } else {
         if (int rc = qmlb::ensure_smem(rff_tc_kernel<K, false>, smem, "qmlb_rff_energy_grad_tc")) return rc;
-        rff_tc_kernel<K, false><<<grid, NTHREADS, smem, st>>>(x, group_start, slot_of_row, nel, packed, atom_energy, grad_x);
+        rff_tc_kernel<K, false><<<grid, NTHREADS, smem, st>>>(x, group_start, slot_of_row, nel, packed, atom_energy, grad_x, seq);
     }
     return qmlb::check_launch("qmlb_rff_energy_grad_tc");
 }
