@@ -432,9 +432,9 @@ def main():
         dist.destroy_process_group()
 
 
-# DRAM bytes per atom of the fused SORF kernel from the ncu capture summarised in
-# profiles/sorf_energy_grad_kernel_c1.md (dram__bytes_read.sum + dram__bytes_write.sum divided by the atoms of the
-# captured launch: 218.3 MB read + 174.2 MB written for 210,000 atoms).
+# DRAM bytes per atom of the fused SORF kernel from an ncu capture of one full-size launch (dram__bytes_read.sum +
+# dram__bytes_write.sum divided by the atoms of the captured launch: 218.3 MB read + 174.2 MB written for 210,000
+# atoms).
 SORF_KERNEL_DRAM_BYTES_PER_ATOM = 1869
 
 if __name__ == '__main__':
