@@ -126,3 +126,31 @@ def test_rff_full_width_properties():
     E, G = _check_invariances(predict, X, Z, c)
     assert cabi.tc_timeouts() == before
     _oracle_sample(X, Z, c, p, model, E, G)
+
+
+def test_normal_equations_full_width_linearity():
+    """Training configuration at full width (npcas 256, nstacks 128: 32,768 features, a 32,768^2 float64 matrix): the
+    normal equations accumulated over 64 conformers in one batch and in two batches of 32 agree to 1e-10 relative, the
+    matrix is symmetric, and Z^T y follows the same split."""
+    import qml_lightning_b200 as q
+    from qml_lightning_b200.utils import synthetic as syn
+    Xn, Zn, cn = syn.conformers(1004, syn.C1_CHARGES, 64)
+    species, npcas, nstacks = [1, 6, 8], 256, 128
+    rep = q.FCHLCuda(species=np.array(species), rcut=6.0, nRs2=24, nRs3=22, eta2=0.32, eta3=2.7, two_body_decay=1.8,
+                     three_body_weight=13.4, three_body_decay=0.57, device=DEV)
+    m = q.HadamardFeaturesModel(rep=rep, elements=np.array(species), ntransforms=1, sigma=2.0, llambda=1e-5, npcas=npcas,
+                                nstacks=nstacks, nbatch_train=64, nbatch_test=64)
+    m.reductors = torch.from_numpy(syn.random_orthonormal_reductors(7, len(species), rep.get_repsize(), npcas)).float().to(DEV)
+    m._parameters_changed()
+    rng = np.random.default_rng(11)
+    Xl, Zl = [x for x in Xn], [z for z in Zn]
+    E = rng.normal(size=64)
+    Fl = [rng.normal(size=(21, 3)) for _ in range(64)]
+    A1, y1 = m.build_Z_components(Xl, Zl, E, Fl, print_info=False)
+    m.nbatch_train = 32
+    A2, y2 = m.build_Z_components(Xl, Zl, E, Fl, print_info=False)
+    scale = float(A1.abs().max())
+    assert scale > 0 and torch.isfinite(A1).all()
+    assert float((A1 - A2).abs().max()) <= 1e-10 * scale
+    assert float((A1 - A1.T).abs().max()) == 0.0
+    assert float((y1 - y2).abs().max()) <= 1e-10 * float(y1.abs().max())
