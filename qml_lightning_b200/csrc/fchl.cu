@@ -172,6 +172,14 @@ __device__ int build_neighbours(const float *sm, float *ws, const FchlK &K, int 
     return nn;
 }
 
+// 2^x on the SFU without the denormal-range fix-up that exp2f() adds (results below 2^-126 flush to zero, which is
+// what a Gaussian tail of that size is worth here); saves three instructions per grid point in the radial loops.
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Row-major enumeration of pairs j<k of n items: t -> (j,k).
 __device__ __forceinline__ void decode_pair(int t, int n, int &j, int &k) {
     const float b = (float)(2 * n - 1);
@@ -305,7 +313,7 @@ fchl_forward_kernel(const float *__restrict__ X, const float *__restrict__ Z, co
                     const float4 b = stage[q];
                     if (lane < K.nRs3) {
                         const float d = b.x - rs;
-                        const float radial = exp2f(c_exp * d * d);
+                        const float radial = ex2_fast(c_exp * d * d);
                         float2 *p2 = reinterpret_cast<float2 *>(acc + __float_as_int(b.w)) + lane;
                         float2 v = *p2;
                         v.x = fmaf(radial, b.y, v.x);
@@ -319,7 +327,7 @@ fchl_forward_kernel(const float *__restrict__ X, const float *__restrict__ Z, co
                     const int sidx = __float_as_int(b.w);
                     for (int l = lane; l < K.nRs3; l += 32) {
                         const float d = b.x - sRs3[l];
-                        const float radial = exp2f(c_exp * d * d);
+                        const float radial = ex2_fast(c_exp * d * d);
                         acc[sidx + 2 * l] += radial * b.y;
                         acc[sidx + 2 * l + 1] += radial * b.z;
                     }
@@ -427,7 +435,7 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
 #pragma unroll BWD_UNROLL
                     for (int l = 0; l < K.nRs3; ++l) {
                         const float d = rbar - sRs3[l];
-                        const float radial = exp2f(c_exp * d * d);
+                        const float radial = ex2_fast(c_exp * d * d);
                         const float2 gg = gb2[l];
                         const float gc = gg.x * radial, gs = gg.y * radial;
                         Gc += gc;
@@ -437,7 +445,7 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
                 } else {
                     for (int l = 0; l < K.nRs3; ++l) {
                         const float d = rbar - sRs3[l];
-                        const float radial = exp2f(c_exp * d * d);
+                        const float radial = ex2_fast(c_exp * d * d);
                         const float gc = gb[2 * l] * radial, gs = gb[2 * l + 1] * radial;
                         Gc += gc;
                         Gs += gs;
