@@ -33,8 +33,8 @@ struct FchlK {
 // ln Rs2 and mu are kept as float pairs (hi + lo): the log-normal exponent (ln Rs2 - mu)^2 / (2 sigma^2) amplifies
 // the rounding of its argument by up to 1/sigma^2 ~ 100, which would otherwise cost a digit of the representation.
 // warp  : NB_FIELDS arrays of A entries | row[repsize] | (backward) force[3A] | 32 x float4 triplet staging
-constexpr int NB_FIELDS = 15;
-enum { F_IDX = 0, F_DX, F_DY, F_DZ, F_R, F_FC, F_DFC, F_ET, F_MU, F_MULO, F_I2S, F_PREF, F_C0, F_C1, F_C2 };
+constexpr int NB_FIELDS = 16;
+enum { F_IDX = 0, F_DX, F_DY, F_DZ, F_R, F_FC, F_DFC, F_ET, F_MU, F_MULO, F_I2S, F_PREF, F_C0, F_C1, F_C2, F_IR };
 
 __host__ __device__ inline int align4(int v) { return (v + 3) & ~3; }
 
@@ -156,6 +156,7 @@ __device__ int build_neighbours(const float *sm, float *ws, const FchlK &K, int 
             ws[F_DY * A + pos] = dy;
             ws[F_DZ * A + pos] = dz;
             ws[F_R * A + pos] = r;
+            ws[F_IR * A + pos] = 1.0f / r;
             ws[F_FC * A + pos] = fc;
             ws[F_DFC * A + pos] = dfc;
             ws[F_MU * A + pos] = (float)mu;
@@ -194,6 +195,7 @@ __device__ __forceinline__ void decode_pair(int t, int n, int &j, int &k) {
 // Scalars of one triplet (i; j,k) that the backward pass needs on top of the forward amplitudes.
 struct TripletGeom {
     float a, b, c;          // r_ij, r_ik, r_jk
+    float ia, ib, ic;       // their reciprocals
     float ci, cj, ck;       // cosines at i, j, k
     float cth, sth, w;      // clamped cos(theta_i), sin(theta_i), regularised 1/sin factor
     float T, R, Fij, Fik;   // ksi3 = w3*T*R ; cut-offs
@@ -207,15 +209,16 @@ __device__ __forceinline__ void triplet_geometry(const float *ws, int A, int j, 
     g.a = ws[F_R * A + j];
     g.b = ws[F_R * A + k];
     const float jx = dxk - dxj, jy = dyk - dyj, jz = dzk - dzj;  // r_j - r_k
-    g.c = sqrtf(jx * jx + jy * jy + jz * jz);
-    const float inv_c = 1.0f / g.c;
+    const float c2 = jx * jx + jy * jy + jz * jz;
+    const float inv_c = rsqrtf(c2);   // SFU reciprocal square root (2 ulp): r_jk only enters well-conditioned factors
+    g.c = c2 * inv_c;
     g.ejk[0] = jx * inv_c;
     g.ejk[1] = jy * inv_c;
     g.ejk[2] = jz * inv_c;
     const float vi = dxj * dxk + dyj * dyk + dzj * dzk;           // (ri-rj).(ri-rk)
     const float vk = jx * dxk + jy * dyk + jz * dzk;              // (rj-rk).(ri-rk)
     const float vj = -(dxj * jx + dyj * jy + dzj * jz);           // (ri-rj).(rk-rj)
-    const float inv_a = 1.0f / g.a, inv_b = 1.0f / g.b;
+    const float inv_a = ws[F_IR * A + j], inv_b = ws[F_IR * A + k];   // 1/r per neighbour, divided once
     g.ci = vi * inv_a * inv_b;
     g.cj = vj * inv_a * inv_c;
     g.ck = vk * inv_b * inv_c;
@@ -227,10 +230,11 @@ __device__ __forceinline__ void triplet_geometry(const float *ws, int A, int j, 
     const float cx = dyj * dzk - dzj * dyk, cy = dzj * dxk - dxj * dzk, cz = dxj * dyk - dyj * dxk;
     const float sab = sqrtf(cx * cx + cy * cy + cz * cz);
     const float ab = g.a * g.b;
-    g.sth = fminf(1.0f, sab / ab);
+    g.sth = fminf(1.0f, sab * inv_a * inv_b);
     g.w = ab / fmaxf(sab, 1e-5f);
+    g.ia = inv_a; g.ib = inv_b; g.ic = inv_c;
     g.T = 1.0f + 3.0f * g.ci * g.cj * g.ck;
-    g.R = exp2f(-K.d3 * __log2f(g.a * g.b * g.c));  // (r_ij r_ik r_jk)^-d3; the SFU log2 is exact to ~2e-7 relative here
+    g.R = ex2_fast(-K.d3 * __log2f(g.a * g.b * g.c));  // (r_ij r_ik r_jk)^-d3; the SFU log2 is exact to ~2e-7 relative here
     g.Fij = ws[F_FC * A + j];
     g.Fik = ws[F_FC * A + k];
     g.dFij = ws[F_DFC * A + j];
@@ -396,7 +400,7 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
                     const float base = pref * sInv2[z] * expf(-t * t * i2s);
                     gr += gb[z] * base * (fc * (c0 + t * (c1 + t * c2)) + dfc);
                 }
-                const float inv_r = 1.0f / ws[F_R * A + jn];
+                const float inv_r = ws[F_IR * A + jn];
                 const float ex = ws[F_DX * A + jn] * inv_r, ey = ws[F_DY * A + jn] * inv_r, ez = ws[F_DZ * A + jn] * inv_r;
                 fi0 += gr * ex;
                 fi1 += gr * ey;
@@ -464,7 +468,7 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
                 g_ci += g_T * 3.0f * g.cj * g.ck;
                 const float g_cj = g_T * 3.0f * g.ci * g.ck;
                 const float g_ck = g_T * 3.0f * g.ci * g.cj;
-                const float inv_a = 1.0f / g.a, inv_b = 1.0f / g.b, inv_c = 1.0f / g.c;
+                const float inv_a = g.ia, inv_b = g.ib, inv_c = g.ic;
                 const float dR = -K.d3 * g.R * g_R;
                 float ga = dR * inv_a + g_Fij * g.dFij + 0.5f * Gr;
                 float gbb = dR * inv_b + g_Fik * g.dFik + 0.5f * Gr;
@@ -584,7 +588,7 @@ fchl_jacobian_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
             const float pref = ws[F_PREF * A + jn];
             const float fc = ws[F_FC * A + jn], dfc = ws[F_DFC * A + jn];
             const float c0 = ws[F_C0 * A + jn], c1 = ws[F_C1 * A + jn], c2 = ws[F_C2 * A + jn];
-            const float inv_r = 1.0f / ws[F_R * A + jn];
+            const float inv_r = ws[F_IR * A + jn];
             const float e[3] = {ws[F_DX * A + jn] * inv_r, ws[F_DY * A + jn] * inv_r, ws[F_DZ * A + jn] * inv_r};
             const int col0 = n_et[jn] * K.nRs2;
             float *Jj = J + (size_t)n_idx[jn] * 3 * R;
@@ -610,7 +614,7 @@ fchl_jacobian_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
             const float Kk = K.w3 * g.T * g.R * g.Fij * g.Fik;
             const float rbar = 0.5f * (g.a + g.b);
             const int sidx = pair_block(n_et[j], n_et[k], K);
-            const float inv_a = 1.0f / g.a, inv_b = 1.0f / g.b, inv_c = 1.0f / g.c;
+            const float inv_a = g.ia, inv_b = g.ib, inv_c = g.ic;
             // derivatives of ci, cj, ck, K with respect to (a, b, c)
             const float dci[3] = {inv_b - g.ci * inv_a, inv_a - g.ci * inv_b, -g.c * inv_a * inv_b};
             const float dcj[3] = {inv_c - g.cj * inv_a, -g.b * inv_a * inv_c, inv_a - g.cj * inv_c};
