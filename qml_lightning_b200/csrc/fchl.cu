@@ -107,7 +107,8 @@ __device__ int stage_molecule(const float *X, const float *Z, const int *counts,
 
 // Builds the neighbour slab of centre atom i for one warp; returns the neighbour count.
 // Per neighbour: index, d = r_i - r_j, r, cut-off fc and its derivative, element, and the two-body scalars
-//   mu, i2s = 1/(2 sigma^2), pref = r^-d2 / (sigma sqrt(2 pi)) (without cut-off),
+//   mu, i2s = log2(e)/(2 sigma^2) (the radial term is evaluated as 2^(-t^2 i2s)), pref = r^-d2 / (sigma sqrt(2 pi))
+//   (without cut-off),
 //   c0,c1,c2: d ln(radial_z)/dr = c0 + c1 t + c2 t^2 with t = ln Rs2[z] - mu (used by the backward pass).
 __device__ int build_neighbours(const float *sm, float *ws, const FchlK &K, int natoms, int i, int lane) {
     const int A = K.A;
@@ -161,7 +162,7 @@ __device__ int build_neighbours(const float *sm, float *ws, const FchlK &K, int 
             ws[F_DFC * A + pos] = dfc;
             ws[F_MU * A + pos] = (float)mu;
             ws[F_MULO * A + pos] = (float)(mu - (double)(float)mu);
-            ws[F_I2S * A + pos] = 0.5f / s2f;
+            ws[F_I2S * A + pos] = 0.5f * 1.4426950408889634f / s2f;
             ws[F_PREF * A + pos] = powf(r, -K.d2) * rsqrtf(s2f) * 0.3989422804014327f;  // 1 / (sigma sqrt(2 pi))
             ws[F_C0 * A + pos] = -0.5f * ds2 / s2f - K.d2 / r;
             ws[F_C1 * A + pos] = dmu / s2f;
@@ -283,7 +284,7 @@ fchl_forward_kernel(const float *__restrict__ X, const float *__restrict__ Z, co
             float *blk = acc + n_et[jn] * K.nRs2;
             for (int z = lane; z < K.nRs2; z += 32) {
                 const float t = (sLog2[z] - mu) + (sLog2lo[z] - mulo);
-                blk[z] += pref * sInv2[z] * expf(-t * t * i2s);
+                blk[z] += pref * sInv2[z] * ex2_fast(-t * t * i2s);
             }
         }
 
@@ -397,7 +398,7 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
                 float gr = 0.f;
                 for (int z = 0; z < K.nRs2; ++z) {
                     const float t = (sLog2[z] - mu) + (sLog2lo[z] - mulo);
-                    const float base = pref * sInv2[z] * expf(-t * t * i2s);
+                    const float base = pref * sInv2[z] * ex2_fast(-t * t * i2s);
                     gr += gb[z] * base * (fc * (c0 + t * (c1 + t * c2)) + dfc);
                 }
                 const float inv_r = ws[F_IR * A + jn];
@@ -594,7 +595,7 @@ fchl_jacobian_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
             float *Jj = J + (size_t)n_idx[jn] * 3 * R;
             for (int z = lane; z < K.nRs2; z += 32) {
                 const float t = (sLog2[z] - mu) + (sLog2lo[z] - mulo);
-                const float base = pref * sInv2[z] * expf(-t * t * i2s);
+                const float base = pref * sInv2[z] * ex2_fast(-t * t * i2s);
                 acc[col0 + z] += base * fc;
                 const float dr = base * (fc * (c0 + t * (c1 + t * c2)) + dfc);
 #pragma unroll
