@@ -434,7 +434,7 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
                 const float a_cos = ZETA2 * Kk * g.cth, a_sin = ZETA2 * Kk * g.sth;
                 const float rbar = 0.5f * (g.a + g.b);
                 const float *gb = grow + pair_block(n_et[j], n_et[k], K);
-                float Gc = 0.f, Gs = 0.f, Gr = 0.f;
+                float Gc = 0.f, Gs = 0.f, Gcd = 0.f, Gsd = 0.f;   // sums of g radial and of g radial (rbar - Rs3)
                 if (pair_ok) {
                     const float2 *gb2 = reinterpret_cast<const float2 *>(gb);
 #pragma unroll BWD_UNROLL
@@ -445,7 +445,8 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
                         const float gc = gg.x * radial, gs = gg.y * radial;
                         Gc += gc;
                         Gs += gs;
-                        Gr = fmaf(fmaf(gc, a_cos, gs * a_sin), d, Gr);
+                        Gcd = fmaf(gc, d, Gcd);
+                        Gsd = fmaf(gs, d, Gsd);
                     }
                 } else {
                     for (int l = 0; l < K.nRs3; ++l) {
@@ -454,10 +455,12 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
                         const float gc = gb[2 * l] * radial, gs = gb[2 * l + 1] * radial;
                         Gc += gc;
                         Gs += gs;
-                        Gr = fmaf(fmaf(gc, a_cos, gs * a_sin), d, Gr);
+                        Gcd = fmaf(gc, d, Gcd);
+                        Gsd = fmaf(gs, d, Gsd);
                     }
                 }
-                Gr *= -2.0f * K.eta3;
+                // the amplitudes are constant over the grid: d/d(rbar) of the radial factor, summed first
+                const float Gr = -2.0f * K.eta3 * fmaf(a_cos, Gcd, a_sin * Gsd);
                 // d/d(cos theta_i), d/dK
                 float g_ci = ZETA2 * Kk * g.w * (Gc * g.sth - Gs * g.cth);
                 const float g_K = ZETA2 * (Gc * g.cth + Gs * g.sth);
