@@ -39,7 +39,8 @@ WORKLOADS = {
     'c3': ([1, 6, 8], 256, 64, 100000, 'RFF model (dense Gaussian projection, 16,384 features) on the 21-atom conformers, weak scaling'),
     'c4': ([1, 6, 8], 256, 128, 512, 'training normal equations: Z^T Z (fp64, 32768^2) over 21-atom conformers, 64 rows each'),
 }
-KERNELS_PER_STEP = 8  # count, scan, assign, fchl forward, pca (tcgen05), sorf fused or rff (tcgen05), pca^T (tcgen05), fchl backward
+# count, scan, assign, fchl forward, 2 x pca pack, pca (tcgen05), sorf fused or rff (tcgen05), pca^T (tcgen05), fchl backward
+KERNELS_PER_STEP = 10
 
 
 def parse_args():
