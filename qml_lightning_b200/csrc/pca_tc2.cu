@@ -208,7 +208,6 @@ pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ p
     const uint32_t tmem_alloc = tmem_slot;
     constexpr uint32_t tmem = 0u;
     const bool tmem_ok = tmem_alloc == 0u;
-    const int ngroups = (nchunks + group_chunks - 1) / group_chunks;
 
     if (warp < WORKER_WARPS) {
         // ------------------------------------------------------------------ A staging + accumulator drain

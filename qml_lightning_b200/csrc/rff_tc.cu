@@ -131,9 +131,8 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void *src, uint32_
 }
 // A shared-memory descriptor is kept as two 32-bit words so that stepping through an operand is one 32-bit add on the
 // low word (start address >> 4 in bits 0-13, leading byte offset >> 4 in bits 16-29); the high word (stride byte
-// offset >> 4, descriptor version 1 at bit 14, no swizzle) never changes.
+// offset >> 4, descriptor version 1 at bit 14, no swizzle) never changes and is a compile-time constant at the call sites.
 __device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) { return ((saddr >> 4) & 0x3FFFu) | ((lbo_bytes >> 4) << 16); }
-__device__ __forceinline__ uint32_t desc_hi(uint32_t sbo_bytes) { return (sbo_bytes >> 4) | (1u << 14); }
 
 // D[tmem] (+)= A[smem] * B[smem]
 __device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint32_t alo, uint32_t ahi, uint32_t blo, uint32_t bhi, uint32_t idesc,
