@@ -137,16 +137,18 @@ __device__ int build_neighbours(const float *sm, float *ws, const FchlK &K, int 
             const int pos = nn + __popc(m & ((1u << lane) - 1u));
             // Distance and the two logarithms of the log-normal parameters in double (their rounding is amplified
             // by 1/sigma^2 in the exponent); everything else is well conditioned and stays in float.
-            const double rd = sqrt((double)dx * dx + (double)dy * dy + (double)dz * dz);
-            const float r = (float)rd;
+            const double r2d = (double)dx * dx + (double)dy * dy + (double)dz * dz;
+            const float r = sqrtf((float)r2d);
             const float inv_rcut = 1.0f / K.rcut;
             float sarg, carg;
             sincospif(r * inv_rcut, &sarg, &carg);
             const float fc = 0.5f * (carg + 1.0f);
             const float dfc = -0.5f * sarg * 3.14159265358979f * inv_rcut;
-            const double eta = (double)K.eta2;
-            const double s2 = log1p(eta / (rd * rd));
-            const double mu = log(rd) - 0.5 * s2;
+            // sigma^2 = ln(1 + eta2 / r^2) = ln(r^2 + eta2) - ln(r^2) ;  mu = ln r - sigma^2 / 2 = ln(r^2) - ln(r^2 + eta2) / 2:
+            // two double logarithms of r^2 and r^2 + eta2 replace sqrt, division, log1p and log of the direct form
+            const double la = log(r2d), lb = log(r2d + (double)K.eta2);
+            const double s2 = lb - la;
+            const double mu = la - 0.5 * lb;
             const float rf2 = r * r;
             const float s2f = (float)s2;
             const float ds2 = -2.0f * K.eta2 / (r * (rf2 + K.eta2));
