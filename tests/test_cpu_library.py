@@ -42,6 +42,29 @@ def test_host_only_entry_points():
     assert b'null' in lib.qmlb_last_error()
 
 
+def test_packing_sizes_of_the_tensor_core_stages():
+    from qml_lightning_b200 import _lib
+    lib = _lib.load()
+    # RFF: 256-byte header + one blob per element and 32-feature chunk: fp16 hi and lo images of [npcas, 32] + 3 x 32 floats
+    assert lib.qmlb_rff_pack_bytes(3, 256, 16384) == 256 + 3 * 512 * (2 * 256 * 32 * 2 + 384)
+    assert lib.qmlb_rff_pack_bytes(3, 256, 1000) == lib.qmlb_rff_pack_bytes(3, 256, 1024)          # features padded to 32
+    assert lib.qmlb_rff_pack_bytes(3, 48, 1024) == 0                                               # unsupported npcas
+    # PCA: per element, column tile and 32-k chunk the hi and lo TF32 images of [tile columns, 32]
+    assert lib.qmlb_pca_pack_bytes(3, 336, 256, 0) == 3 * 1 * 11 * (2 * 256 * 32 * 4)              # 336 -> 11 chunks
+    assert lib.qmlb_pca_pack_bytes(3, 336, 256, 1) == 3 * 2 * 8 * (2 * 176 * 32 * 4)               # 336 columns -> 2 tiles of 176
+    assert lib.qmlb_pca_pack_bytes(5, 780, 128, 1) == 5 * 4 * 4 * (2 * 208 * 32 * 4)               # 780 columns -> 4 tiles of 208
+    assert lib.qmlb_pca_pack(None, 3, 336, 256, 0, None, 0, None) == 1 and b'null' in lib.qmlb_last_error()
+
+
+def test_missing_library_is_an_error_not_a_fallback(tmp_path):
+    import subprocess
+    import sys
+    env = dict(os.environ, QMLB200_LIB=str(tmp_path / 'nowhere' / 'libqmlb200.so'))
+    r = subprocess.run([sys.executable, '-c', 'from qml_lightning_b200 import _lib; _lib.load()'], cwd=ROOT, env=env,
+                       capture_output=True, text=True)
+    assert r.returncode != 0 and 'no CPU or PyTorch fallback' in r.stderr
+
+
 def test_torch_operator_schemas_match_upstream_argument_lists():
     import qml_lightning_b200  # noqa: F401
     get = torch._C._jit_get_schemas_for_operator
