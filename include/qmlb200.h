@@ -115,13 +115,18 @@ int qmlb_fchl19_forward_jacobian(const float *X, const float *Z, const int *atom
 
 /* Rows of the per-atom work arrays are ordered by model element, each element group padded to a multiple of
  * QMLB_ROW_TILE rows.  Given Z and the model's `elements` (f32[nelements] charges) this writes
- *   row_of_slot i32[nb*A]        row of atom (m,a) or -1 (padding / element not in `elements`)
+ *   row_of_slot i32[nb*A]        row of atom (m,a), -1 (padding / element not in `elements`) or
+ *                                QMLB_ROW_OVERFLOW (a real atom for which rows_cap had no row left)
  *   slot_of_row i32[rows_cap]    m*A+a of a row, -1 for padding rows
  *   group_start i32[nelements+1] first row of each element group (group_start[nelements] = rows in use)
  * Within a group rows follow (m,a) order, so the result is deterministic.
- * rows_cap must be >= qmlb_rows_capacity(n_atoms_upper, nelements).  `scratch` is
- * qmlb_group_scratch_bytes(nb, nelements) bytes of device memory. */
+ * rows_cap must be >= qmlb_rows_capacity(n_atoms_upper, nelements) with n_atoms_upper >= the number of real
+ * atoms.  The host cannot check that bound without waiting for the device, so the device does: atoms beyond the
+ * capacity are marked QMLB_ROW_OVERFLOW, nothing is written out of bounds, and qmlb_fchl19_backward (hence
+ * qmlb_sorf_predict / qmlb_rff_predict*) returns NaN energies and gradients for every molecule that holds such an
+ * atom.  `scratch` is qmlb_group_scratch_bytes(nb, nelements) bytes of device memory. */
 #define QMLB_ROW_TILE 128
+#define QMLB_ROW_OVERFLOW (-2)
 size_t qmlb_rows_capacity(size_t n_atoms_upper, int nelements);
 size_t qmlb_group_scratch_bytes(int nb, int nelements);
 int qmlb_group_by_element(const float *Z, const int *atom_counts, const float *elements, int nelements, int nb,

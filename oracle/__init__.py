@@ -12,9 +12,10 @@ line range whose arithmetic it restates.
 
 Parity pin: ``tests/test_oracle_kat.py`` feeds the oracle with the tensors of
 the upstream TorchScript fixture ``unit_tests/models/saved_models/model_sorf.pt``
-and the geometry / expected energy / expected forces parsed at test time from
-``unit_tests/models/unit_test_sorf.py`` and applies that script's own
-``np.isclose`` criteria.  The RFF and training (Z^T Z) restatements have no
+and the geometry / expected energy / expected forces parsed from
+``unit_tests/models/unit_test_sorf.py`` (both committed under
+``tests/golden/upstream/``) and applies that script's own ``np.isclose``
+criteria.  The RFF and training (Z^T Z) restatements have no
 upstream fixture: their parity is unpinned by upstream tests and rests on the
 shared FCHL19/PCA front end plus self-consistency checks.
 """
@@ -22,6 +23,9 @@ shared FCHL19/PCA front end plus self-consistency checks.
 from .qml_oracle import (  # noqa: F401
     FCHLParams,
     fchl19_representation,
+    minimum_image,
+    neighbour_lists,
+    kahan_gram,
     fwht,
     sorf_coefficients,
     sorf_energy,

@@ -3,8 +3,9 @@
 The upstream project pins its whole inference chain with one script,
 ``unit_tests/models/unit_test_sorf.py`` (geometry, charges, expected energy and
 forces as Python literals) plus a TorchScript archive
-``unit_tests/models/saved_models/model_sorf.pt``.  Neither is copied into this
-repository: both are read from an upstream checkout at test time.
+``unit_tests/models/saved_models/model_sorf.pt``.  ``tests/golden/upstream/``
+holds a copy of the archive and the parsed literals, written by
+``tests/golden/upstream/make_upstream_golden.py`` with the readers below.
 
 * ``load_torchscript_tensors`` decodes the archive without registering any
   custom operator and without a GPU: the archive is a zip, ``data.pkl`` is a

@@ -11,6 +11,8 @@ Upstream files restated here (paths inside the upstream project):
   qml_lightning/cuda/fchl_cuda_kernel.cu:1716-1742   element index = position in ``species``
   qml_lightning/cuda/pairlist_kernel.cu:372-390      neighbour rule 0 < r^2 < rcut^2
   qml_lightning/cuda/fchl_cuda_kernel.cu:476-674     two-body and three-body terms
+  qml_lightning/cuda/fchl_cuda_kernel.cu:16-49 and
+  qml_lightning/cuda/pairlist_kernel.cu:6-39         minimum-image convention of periodic cells
   qml_lightning/representations/dimensionality_reduction.py:47-58   PCA projection
   qml_lightning/cuda/hadamard_kernel.cu:5-102        [HD]^T transform, 2^(-log2N/2) per H
   qml_lightning/cuda/hadamard_kernel.cu:778-800      cos features, sqrt(2/F), per-molecule sum
@@ -18,6 +20,8 @@ Upstream files restated here (paths inside the upstream project):
   qml_lightning/models/random_features.py:69-102     RFF model forward
   qml_lightning/cuda/hadamard_kernel.cu:565-717 and
   qml_lightning/models/kernel.py:119-124,164-170     training rows: G = -dZ/dr
+  qml_lightning/cuda/utils_kernel.cu:70-129 and
+  qml_lightning/models/kernel.py:176-188             float32 Kahan product accumulated in float64
 """
 
 from __future__ import annotations
@@ -79,7 +83,17 @@ def element_types(Z: torch.Tensor, species: Sequence[int]) -> torch.Tensor:
     return et
 
 
-def _fchl_chunk(X, Z, counts, p: FCHLParams):
+def minimum_image(d, cell, inv_cell):
+    """get_pbc_drij (fchl_cuda_kernel.cu:16-49, pairlist_kernel.cu:6-39): ``s = inv_cell . d``, ``s -= round(s)``,
+    ``d = cell . s`` with the row-major 3x3 matrices of each molecule; ``d [nb, ..., 3]``, ``cell [nb,3,3]``."""
+    shape = d.shape
+    flat = d.reshape(shape[0], -1, 3)
+    s = torch.einsum('bmk,bnk->bnm', inv_cell.to(d.dtype), flat)
+    s = s - torch.round(s)
+    return torch.einsum('bmk,bnk->bnm', cell.to(d.dtype), s).reshape(shape)
+
+
+def _fchl_chunk(X, Z, counts, p: FCHLParams, cell=None, inv_cell=None):
     nb, A, _ = X.shape
     dt = X.dtype
     nel = p.nspecies
@@ -94,6 +108,8 @@ def _fchl_chunk(X, Z, counts, p: FCHLParams):
     known = real & (et >= 0)
 
     d = X[:, :, None, :] - X[:, None, :, :]                         # d[b,a,c] = r_a - r_c
+    if cell is not None:
+        d = minimum_image(d, cell, inv_cell)                        # :375-377, :414-416 (every r_i - r_j, r_i - r_k)
     r2 = (d * d).sum(-1)
     offdiag = ar[:, None] != ar[None, :]
     pair_ok = known[:, :, None] & known[:, None, :] & offdiag[None]
@@ -118,12 +134,16 @@ def _fchl_chunk(X, Z, counts, p: FCHLParams):
 
     # ---- three-body, fchl_cuda_kernel.cu:605-672 (pairs j<k of the neighbour list of i)
     tri = nbr[:, :, :, None] & nbr[:, :, None, :] & (ar[:, None] < ar[None, :])[None, None]
+    # the third side of a triplet is the difference of the two (minimum-image) vectors from the centre atom,
+    # drjk = drik - drij = r_j - r_k (:617-619); without a cell this is r[b,j,k]
+    vjk = d[:, :, None, :, :] - d[:, :, :, None, :]                 # [b,i,j,k,:]
+    rjk2 = (vjk * vjk).sum(-1)
+    rjk = torch.sqrt(torch.where(tri, rjk2, torch.ones_like(rjk2)))
     dots_i = torch.einsum('bijx,bikx->bijk', d, d)                  # (ri-rj).(ri-rk)
-    dots_j = torch.einsum('bjix,bjkx->bijk', d, d)                  # (rj-ri).(rj-rk)
-    dots_k = torch.einsum('bkix,bkjx->bijk', d, d)                  # (rk-ri).(rk-rj)
+    dots_j = -torch.einsum('bijx,bijkx->bijk', d, vjk)              # (ri-rj).(rk-rj): angle at j (:649)
+    dots_k = torch.einsum('bikx,bijkx->bijk', d, vjk)               # (ri-rk).(rj-rk): angle at k (:647)
     rij = r[:, :, :, None]
     rik = r[:, :, None, :]
-    rjk = r[:, None, :, :]
     one = torch.ones_like(dots_i)
     zero = torch.zeros_like(dots_i)
     cos_i = torch.where(tri, dots_i / (rij * rik), zero)
@@ -155,20 +175,42 @@ def _fchl_chunk(X, Z, counts, p: FCHLParams):
 
 
 def fchl19_representation(X: torch.Tensor, Z: torch.Tensor, atom_counts: torch.Tensor, p: FCHLParams,
-                          chunk: Optional[int] = None) -> torch.Tensor:
+                          chunk: Optional[int] = None, cell: Optional[torch.Tensor] = None,
+                          inv_cell: Optional[torch.Tensor] = None) -> torch.Tensor:
     """FCHL19 representation ``[nb, A, repsize]``; padded atoms are zero rows.
 
     Restates fchl19_representation_cuda (fchl_cuda_kernel.cu:476-674) with the
-    neighbour rule of pairlist_kernel.cu:372-390.  Non-periodic only.
+    neighbour rule of pairlist_kernel.cu:372-390.  ``cell`` / ``inv_cell``
+    ``[nb,3,3]`` switch on the minimum-image convention (an atom sees at most one
+    image of every other atom and never its own images, as upstream).
     """
     nb, A, _ = X.shape
+    if cell is not None and cell.numel() == 0:
+        cell = inv_cell = None
     if chunk is None:
         per_mol = max(1, A * A * A * p.nRs3 * 6)
         chunk = max(1, int(6e7 // per_mol))
     out = []
     for s in range(0, nb, chunk):
-        out.append(_fchl_chunk(X[s:s + chunk], Z[s:s + chunk], atom_counts[s:s + chunk], p))
+        out.append(_fchl_chunk(X[s:s + chunk], Z[s:s + chunk], atom_counts[s:s + chunk], p,
+                               None if cell is None else cell[s:s + chunk],
+                               None if cell is None else inv_cell[s:s + chunk]))
     return torch.cat(out, dim=0) if out else X.new_zeros((0, A, p.repsize))
+
+
+def neighbour_lists(X, atom_counts, rcut, cell=None, inv_cell=None):
+    """``(counts i64[nb,A], lists: nb x A python lists)``: neighbours j != i with 0 < r^2 < rcut^2 in ascending j
+    (pairlist_kernel.cu:145-224, 326-391), minimum image when a cell is given."""
+    nb, A, _ = X.shape
+    d = X[:, :, None, :] - X[:, None, :, :]
+    if cell is not None and cell.numel():
+        d = minimum_image(d, cell, inv_cell)
+    r2 = (d * d).sum(-1)
+    ar = torch.arange(A)
+    real = ar[None, :] < atom_counts[:, None].long()
+    ok = real[:, :, None] & real[:, None, :] & (ar[:, None] != ar[None, :])[None] & (r2 > 0) & (r2 < rcut * rcut)
+    lists = [[torch.where(ok[b, i])[0].tolist() for i in range(A)] for b in range(nb)]
+    return ok.sum(-1), lists
 
 
 def fwht(x: torch.Tensor) -> torch.Tensor:
@@ -245,7 +287,7 @@ def rff_energy(rep, Z, counts, elements, reductors, W, b, alpha):
 
 
 def energy_and_forces(X, Z, counts, p: FCHLParams, model: dict, batch: int = 64, forces: bool = True,
-                      dtype=torch.float64):
+                      dtype=torch.float64, cell=None, inv_cell=None):
     """Energies ``[nb]`` and forces ``-dE/dX`` ``[nb,A,3]`` in host batches.
 
     ``model`` holds ``kind`` ('sorf' | 'rff'), ``elements``, ``reductors`` and
@@ -259,7 +301,8 @@ def energy_and_forces(X, Z, counts, p: FCHLParams, model: dict, batch: int = 64,
         x = X[s:s + batch].to(dtype).clone().requires_grad_(forces)
         z = Z[s:s + batch]
         c = counts[s:s + batch]
-        rep = fchl19_representation(x, z, c, p)
+        rep = fchl19_representation(x, z, c, p, cell=None if cell is None else cell[s:s + batch],
+                                    inv_cell=None if cell is None else inv_cell[s:s + batch])
         if model['kind'] == 'sorf':
             E, _ = sorf_energy(rep, z, c, model['elements'], model['reductors'], model['Dmat'], model['bias'],
                                model['alpha'], model['sigma'], model['ntransforms'])
@@ -274,7 +317,7 @@ def energy_and_forces(X, Z, counts, p: FCHLParams, model: dict, batch: int = 64,
     return (E, torch.cat(Fs)) if forces else E
 
 
-def training_rows(X, Z, counts, p: FCHLParams, model: dict, dtype=torch.float64):
+def training_rows(X, Z, counts, p: FCHLParams, model: dict, dtype=torch.float64, cell=None, inv_cell=None):
     """Training rows for small cases: ``Zrows [nb,F]`` and ``G [nb,A,3,F] = -dZ/dr``.
 
     kernel.py:134-170 builds exactly these (energy rows, then one row per atom
@@ -283,7 +326,7 @@ def training_rows(X, Z, counts, p: FCHLParams, model: dict, dtype=torch.float64)
     only with a few hundred features.
     """
     x = X.to(dtype).clone().requires_grad_(True)
-    rep = fchl19_representation(x, Z, counts, p)
+    rep = fchl19_representation(x, Z, counts, p, cell=cell, inv_cell=inv_cell)
     if model['kind'] == 'sorf':
         _, Zf = sorf_energy(rep, Z, counts, model['elements'], model['reductors'], model['Dmat'], model['bias'],
                             torch.zeros(model['Dmat'].shape[2] * model['reductors'].shape[-1]), model['sigma'],
@@ -297,3 +340,23 @@ def training_rows(X, Z, counts, p: FCHLParams, model: dict, dtype=torch.float64)
         g, = torch.autograd.grad(Zf[:, f].sum(), x, retain_graph=True)
         G[..., f] = -g
     return Zf.detach(), G
+
+
+def kahan_gram(M: torch.Tensor) -> torch.Tensor:
+    """``M^T M`` the way ``use_specialized_matmul`` computes it upstream: build_Z_components passes
+    ``Ztrain.float().T`` and ``Ztrain.float()`` (kernel.py:176-188) to matmul_and_reduce_kernel
+    (utils_kernel.cu:70-129), which forms every entry as a Kahan-compensated float32 sum over the rows, each term
+    entering through ``fma(a, b, -c)``, and adds ``(double) sum`` to the float64 matrix.  Returned as float64
+    ``[F, F]`` (the contribution of one row block).  The fma is restated as a float64 product (exact for float32
+    factors) minus ``c``, rounded once to float32."""
+    import numpy as np
+    A = M.to(torch.float32).double().numpy()
+    F = A.shape[1]
+    total = np.zeros((F, F), dtype=np.float32)
+    c = np.zeros((F, F), dtype=np.float32)
+    for k in range(A.shape[0]):
+        y = (np.outer(A[k], A[k]) - c.astype(np.float64)).astype(np.float32)
+        t = total + y
+        c = (t - total) - y
+        total = t
+    return torch.from_numpy(total.astype(np.float64))

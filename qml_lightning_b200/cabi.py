@@ -5,7 +5,7 @@ PyTorch is used only as the owner of device memory and of the current CUDA strea
 the C entry point of the same name (``qmlb_<name>``).  No arithmetic happens in Python.
 """
 import ctypes
-import math
+import functools
 
 import torch
 
@@ -290,11 +290,14 @@ _workspaces = {}
 
 
 def _workspace(device, nbytes):
-    """Grow-only per-device scratch buffer, so steady-state prediction allocates nothing."""
-    ws = _workspaces.get(device)
+    """Grow-only scratch buffer per (device, stream), so steady-state prediction allocates nothing and predictions
+    issued on different streams never share scratch.  A buffer that is outgrown goes back to the caching allocator,
+    which keeps it away from other streams until the work queued on its own stream has finished."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(int(nbytes * 1.1) + 256, dtype=torch.uint8, device=device)
-        _workspaces[device] = ws
+        _workspaces[key] = ws
     return ws
 
 
@@ -488,3 +491,27 @@ def rff_train_features(x, dx, W, b, grouping, atom_counts, nb, A):
                                               grouping.rows_cap, K, D, _p(Z), _p(G), _p(arg), _p(T), _stream(dev)),
           'qmlb_rff_train_features')
     return Z, G
+
+
+def _on_tensor_device(fn):
+    """Run ``fn`` with the device of its first CUDA tensor argument current: kernel launches, per-device caches
+    inside the library (cuBLAS handle, built-in scratch address) and ``cudaFuncSetAttribute`` all act on the current
+    device, which need not be the one the caller's tensors live on."""
+    @functools.wraps(fn)
+    def wrapped(*args, **kwargs):
+        for a in list(args) + list(kwargs.values()):
+            t = a.row_of_slot if isinstance(a, Grouping) else (a.species if isinstance(a, FchlKernelParams) else a)
+            if isinstance(t, torch.Tensor) and t.is_cuda:
+                if t.device.index == torch.cuda.current_device():
+                    break
+                with torch.cuda.device(t.device):
+                    return fn(*args, **kwargs)
+        return fn(*args, **kwargs)
+    return wrapped
+
+
+for _name, _fn in list(globals().items()):
+    if callable(_fn) and getattr(_fn, '__module__', None) == __name__ and not _name.startswith('_') \
+            and not isinstance(_fn, type) and _name not in ('tc_timeouts',):
+        globals()[_name] = _on_tensor_device(_fn)
+del _name, _fn

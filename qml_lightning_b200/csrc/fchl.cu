@@ -63,6 +63,21 @@ __device__ __forceinline__ void min_image(float &dx, float &dy, float &dz, const
     dz = cell[6] * s0 + cell[7] * s1 + cell[8] * s2;
 }
 
+// The same in double for the FCHL19 kernels: the stored coordinates of a periodic system may lie several cell lengths
+// apart, so r_i - r_j and its reduction are formed in double (both are exact or nearly so) and rounded to float once;
+// the reduced vector then carries the same relative rounding as in the non-periodic case.
+__device__ __forceinline__ void min_image_d(double &dx, double &dy, double &dz, const float *cell, const float *icell) {
+    double s0 = (double)icell[0] * dx + (double)icell[1] * dy + (double)icell[2] * dz;
+    double s1 = (double)icell[3] * dx + (double)icell[4] * dy + (double)icell[5] * dz;
+    double s2 = (double)icell[6] * dx + (double)icell[7] * dy + (double)icell[8] * dz;
+    s0 -= round(s0);
+    s1 -= round(s1);
+    s2 -= round(s2);
+    dx = (double)cell[0] * s0 + (double)cell[1] * s1 + (double)cell[2] * s2;
+    dy = (double)cell[3] * s0 + (double)cell[4] * s1 + (double)cell[5] * s2;
+    dz = (double)cell[6] * s0 + (double)cell[7] * s1 + (double)cell[8] * s2;
+}
+
 __device__ __forceinline__ int species_index(float z, const float *species, int nel) {
     // upstream truncates the charge to int and keeps the last match (fchl_cuda_kernel.cu:1730-1737)
     float q = (float)(int)z;
@@ -125,10 +140,17 @@ __device__ int build_neighbours(const float *sm, float *ws, const FchlK &K, int 
         bool ok = false;
         float dx = 0.f, dy = 0.f, dz = 0.f, r2 = 0.f;
         if (j < natoms && j != i && set[j] >= 0) {
-            dx = xi - sx[j];
-            dy = yi - sy[j];
-            dz = zi - sz[j];
-            if (K.pbc) min_image(dx, dy, dz, scell, scell + 9);
+            if (K.pbc) {
+                double ddx = (double)xi - (double)sx[j], ddy = (double)yi - (double)sy[j], ddz = (double)zi - (double)sz[j];
+                min_image_d(ddx, ddy, ddz, scell, scell + 9);
+                dx = (float)ddx;
+                dy = (float)ddy;
+                dz = (float)ddz;
+            } else {
+                dx = xi - sx[j];
+                dy = yi - sy[j];
+                dz = zi - sz[j];
+            }
             r2 = dx * dx + dy * dy + dz * dz;
             ok = r2 < rcut2 && r2 > 0.f;  // cuda/pairlist_kernel.cu:386
         }
@@ -532,13 +554,20 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
         }
         __syncwarp();
     }
-    __syncthreads();
+    // an atom that found no row because the caller's row capacity was too small poisons its molecule: NaN energy and
+    // gradient instead of a silently incomplete sum
+    int lost = 0;
+    if (row_of_slot)
+        for (int a = threadIdx.x; a < natoms; a += blockDim.x) lost |= row_of_slot[(size_t)mol * A + a] == QMLB_ROW_OVERFLOW;
+    lost = __syncthreads_or(lost);
+    const float poison = lost ? __int_as_float(0x7fc00000) : 0.f;
     // fixed-order reduction over the warps' partial gradients
     for (int c = threadIdx.x; c < 3 * A; c += blockDim.x) {
         float s = 0.f;
         if (c < 3 * natoms) {
 #pragma unroll
             for (int w = 0; w < FCHL_WARPS; ++w) s += sm[L.block_floats + (size_t)w * L.warp_floats + L.off_force + c];
+            s += poison;
         }
         grad_X[(size_t)mol * 3 * A + c] = s;
     }
@@ -548,7 +577,7 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
             const long row = row_of_slot ? (long)row_of_slot[(size_t)mol * A + a] : (long)mol * A + a;
             if (row >= 0) e += atom_energy[row];
         }
-        e = warp_sum(e);
+        e = warp_sum(e) + poison;
         if (lane == 0) mol_energy[mol] = e;
     }
 }

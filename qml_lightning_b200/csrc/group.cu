@@ -112,7 +112,9 @@ __global__ void assign_kernel(const float *__restrict__ Z, const int *__restrict
             next[q] += __popc(msk);
         }
         if (s < s1) {
-            if (row >= rows_cap) row = -1;  // capacity is validated by the host; never write out of bounds
+            // a row capacity below the real atom count cannot be seen by the host without a synchronisation: such atoms
+            // are marked, and the kernels that produce energies and gradients turn the mark into NaN for their molecule
+            if (row >= rows_cap) row = QMLB_ROW_OVERFLOW;
             row_of_slot[s] = row;
             if (row >= 0) slot_of_row[row] = (int)s;
         }
