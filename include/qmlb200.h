@@ -230,11 +230,18 @@ int qmlb_sorf_energy_grad(const float *x, const int *group_start, const int *slo
  * (qmlb_predict_workspace_bytes bytes, 256-byte aligned device memory); nothing is allocated and the host never
  * waits for the device.  n_atoms_upper is an upper bound of the number of real atoms (nb*A if unknown; the length
  * of upstream's atomIDs tensor when available).  elements f32[nelements] are the model's elements,
- * reductors f32[nelements, repsize, npcas], packed from qmlb_sorf_pack. */
+ * reductors f32[nelements, repsize, npcas], packed from qmlb_sorf_pack.  pca_packed (optional, NULL = build the images
+ * inside the workspace on every call) are the split and tiled images of the projection matrices for both directions,
+ * made once per model by qmlb_pca_pair_pack into qmlb_pca_pair_pack_bytes bytes of 256-byte aligned device memory; with
+ * it `reductors` is not read. */
+size_t qmlb_pca_pair_pack_bytes(int nelements, int repsize, int npcas);
+int qmlb_pca_pair_pack(const float *reductors, int nelements, int repsize, int npcas, void *pca_packed, size_t packed_bytes,
+                       qmlb_stream_t stream);
 size_t qmlb_predict_workspace_bytes(int nb, int A, size_t n_atoms_upper, int nelements, int repsize, int npcas);
 int qmlb_sorf_predict(const float *X, const float *Z, const int *atom_counts, int nb, int A, const qmlb_fchl_params *p,
                       const float *cell, const float *inv_cell, const float *elements, int nelements,
-                      const float *reductors, int npcas, const void *packed, int S, int T, float sigma, int fast_math,
+                      const float *reductors, const void *pca_packed, int npcas, const void *packed, int S, int T, float sigma,
+                      int fast_math,
                       size_t n_atoms_upper, void *workspace, size_t workspace_bytes, float *energy, float *grad_X,
                       qmlb_stream_t stream);
 
@@ -267,7 +274,8 @@ int qmlb_rff_energy_grad_tc(const float *x, const int *group_start, const int *s
  * same conventions and workspace as qmlb_sorf_predict. */
 int qmlb_rff_predict(const float *X, const float *Z, const int *atom_counts, int nb, int A, const qmlb_fchl_params *p,
                      const float *cell, const float *inv_cell, const float *elements, int nelements,
-                     const float *reductors, int npcas, const float *W, const float *b, const float *alpha, int nfeatures,
+                     const float *reductors, const void *pca_packed, int npcas, const float *W, const float *b,
+                     const float *alpha, int nfeatures,
                      int fast_math, size_t n_atoms_upper, void *workspace, size_t workspace_bytes, float *energy,
                      float *grad_X, qmlb_stream_t stream);
 
@@ -275,7 +283,8 @@ int qmlb_rff_predict(const float *X, const float *Z, const int *atom_counts, int
  * (qmlb_rff_energy_grad_tc).  This is the path RandomFourrierFeaturesModel uses. */
 int qmlb_rff_predict_packed(const float *X, const float *Z, const int *atom_counts, int nb, int A, const qmlb_fchl_params *p,
                             const float *cell, const float *inv_cell, const float *elements, int nelements,
-                            const float *reductors, int npcas, const void *packed, int fast_math, size_t n_atoms_upper,
+                            const float *reductors, const void *pca_packed, int npcas, const void *packed, int fast_math,
+                            size_t n_atoms_upper,
                             void *workspace, size_t workspace_bytes, float *energy, float *grad_X, qmlb_stream_t stream);
 
 /* Projection of an element-grouped explicit Jacobian: project_derivative = einsum('jmnk,kl->jmnl')
@@ -297,6 +306,25 @@ int qmlb_sorf_train_features(const float *x, const float *dx, const float *Dmat,
                              int A, size_t rows_cap, int N, int S, int T, float sigma, double *Zout, double *G,
                              float *sinc_scratch, qmlb_stream_t stream);
 
+/* The fine-grained SORF training operators of the upstream extension module sorf_gpu (cuda/hadamard_cuda.cpp:77-126),
+ * for scripts that drive upstream's per-element calculate_features themselves (models/hadamard_features.py:66-80).
+ * They work on the n rows of ONE element, take the molecule of every row from ordering i32[n] and ACCUMULATE into
+ * caller-owned float64 tensors (float64 atomics, like upstream), which must therefore be initialised by the caller.
+ *   qmlb_hadamard_features_accumulate: compute_hadamard_features / compute_featurisation_kernel
+ *     (cuda/hadamard_kernel.cu:541-563): features f64[nmol,F] += sqrt(2/F) cos(coeffs f32[n,F] + bias f32[F]).
+ *   qmlb_partial_feature_derivatives: compute_partial_feature_derivatives / compute_sin_coeffs_kernel (:565-585):
+ *     out f64[n,F] = sqrt(2/F) sin(coeffs + bias)  (overwritten).
+ *   qmlb_featurization_derivative_accumulate: compute_molecular_featurization_derivative /
+ *     compute_featurisation_derivative_kernel (:587-717): feature_derivatives f64[nmol,A,3,F] +=
+ *     normalisation * partial_derivatives[a,f] * [N^(-T/2) (H D_{T-1} ... H D_0) input_derivatives[a,j,x,:]]_f,
+ *     D f32[T,S,N], input_derivatives f32[n,A,3,N]. */
+int qmlb_hadamard_features_accumulate(const float *coeffs, const float *bias, const int *ordering, int n, int F,
+                                      double *features, qmlb_stream_t stream);
+int qmlb_partial_feature_derivatives(const float *coeffs, const float *bias, int n, int F, double *out, qmlb_stream_t stream);
+int qmlb_featurization_derivative_accumulate(const double *partial_derivatives, double normalisation, const float *D,
+                                             const float *input_derivatives, const int *ordering, int n, int A, int N, int S,
+                                             int T, double *feature_derivatives, qmlb_stream_t stream);
+
 /* RFF training features of one batch: random_fourrier_features_kernel / _derivative
  * (cuda/random_features_kernel.cu:5-94) via get_rff / get_rff_derivatives (cuda/random_features.cpp:11-33), as
  * driven by RandomFourrierFeaturesModel.calculate_features (models/random_features.py:60-67), for all elements
@@ -310,10 +338,26 @@ int qmlb_rff_train_features(const float *x, const float *dx, const float *W, con
 
 /* ZTZ += M^T M (row-major UPPER triangle only) and ZTy += M^T y for a row block M f64[rows,F]:
  * torch.matmul(Ztrain.T, Ztrain) / torch.matmul(Ztrain.T, targets) in build_Z_components (models/kernel.py:172-192).
- * cuBLAS DSYRK + DGEMV on `stream`.  qmlb_symmetrize_upper mirrors the triangle before the solve. */
+ * In-tree float64 kernels: qmlb_syrk_f64 (mma.sync.m8n8k4.f64 tiles of the upper triangle) and qmlb_gemv_t_f64
+ * (float64 atomics over row splits: ZTy is reproducible to rounding, not bitwise).  qmlb_symmetrize_upper mirrors the
+ * triangle before the solve.  qmlb_normal_equations_accumulate_cublas is the same update through cuBLAS DSYRK + DGEMV,
+ * kept so that the in-tree kernel can be timed against the library in the same process. */
 int qmlb_normal_equations_accumulate(const double *M, int rows, int F, const double *y, double *ZTZ, double *ZTy,
                                      qmlb_stream_t stream);
+int qmlb_normal_equations_accumulate_cublas(const double *M, int rows, int F, const double *y, double *ZTZ, double *ZTy,
+                                            qmlb_stream_t stream);
+int qmlb_syrk_f64(const double *M, int rows, int F, double *ZTZ, qmlb_stream_t stream);
+int qmlb_gemv_t_f64(const double *M, int rows, int F, const double *y, double *ZTy, qmlb_stream_t stream);
 int qmlb_symmetrize_upper(double *ZTZ, int F, qmlb_stream_t stream);
+
+/* Packed form of the accumulated upper triangle for the exchange between ranks: the sum of the per-rank partial
+ * matrices (one all-reduce where upstream has a single device, models/kernel.py:46-217) needs only the F(F+1)/2
+ * entries that were accumulated, half the bytes of the square matrix.  packed f64[qmlb_packed_upper_elements(F)]:
+ * row i holds columns i..F-1 and starts at i*F - i*(i-1)/2.  qmlb_unpack_upper writes the triangle back and mirrors
+ * it (the matrix is symmetric again afterwards).  F <= 65535. */
+size_t qmlb_packed_upper_elements(int F);
+int qmlb_pack_upper(const double *ZTZ, int F, double *packed, qmlb_stream_t stream);
+int qmlb_unpack_upper(const double *packed, int F, double *ZTZ, qmlb_stream_t stream);
 
 #ifdef __cplusplus
 }

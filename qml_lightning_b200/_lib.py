@@ -50,8 +50,10 @@ SIGNATURES = {
     'qmlb_sorf_pack': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     'qmlb_sorf_energy_grad': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     'qmlb_predict_workspace_bytes': (c_size_t, [c_int, c_int, c_size_t, c_int, c_int, c_int]),
+    'qmlb_pca_pair_pack_bytes': (c_size_t, [c_int, c_int, c_int]),
+    'qmlb_pca_pair_pack': (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     'qmlb_sorf_predict': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, P, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                  c_int, c_void_p, c_int, c_int, c_float, c_int, c_size_t, c_void_p, c_size_t, c_void_p,
+                                  c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int, c_size_t, c_void_p, c_size_t, c_void_p,
                                   c_void_p, c_void_p]),
     'qmlb_rff_energy_grad': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                      c_int, c_void_p, c_void_p, c_void_p]),
@@ -60,18 +62,28 @@ SIGNATURES = {
     'qmlb_rff_energy_grad_tc': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                         c_void_p]),
     'qmlb_rff_predict': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, P, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                 c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_size_t, c_void_p, c_size_t, c_void_p,
+                                 c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_size_t, c_void_p, c_size_t, c_void_p,
                                  c_void_p, c_void_p]),
     'qmlb_rff_predict_packed': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, P, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                        c_int, c_void_p, c_int, c_size_t, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]),
+                                        c_void_p, c_int, c_void_p, c_int, c_size_t, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]),
     'qmlb_pca_project_jacobian': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_int, c_int, c_int, c_void_p, c_void_p]),
     'qmlb_sorf_train_features': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                          c_int, c_int, c_size_t, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p,
                                          c_void_p]),
     'qmlb_rff_train_features': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                         c_int, c_size_t, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    'qmlb_hadamard_features_accumulate': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    'qmlb_partial_feature_derivatives': (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    'qmlb_featurization_derivative_accumulate': (c_int, [c_void_p, ctypes.c_double, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                         c_int, c_int, c_void_p, c_void_p]),
     'qmlb_normal_equations_accumulate': (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    'qmlb_normal_equations_accumulate_cublas': (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    'qmlb_syrk_f64': (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    'qmlb_gemv_t_f64': (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     'qmlb_symmetrize_upper': (c_int, [c_void_p, c_int, c_void_p]),
+    'qmlb_packed_upper_elements': (c_size_t, [c_int]),
+    'qmlb_pack_upper': (c_int, [c_void_p, c_int, c_void_p, c_void_p]),
+    'qmlb_unpack_upper': (c_int, [c_void_p, c_int, c_void_p, c_void_p]),
 }
 
 _lib = None

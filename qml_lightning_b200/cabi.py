@@ -160,6 +160,43 @@ class Grouping:
         self.rows_cap, self.nelements = rows_cap, nelements
 
 
+def grouping_from_ordering(ordering, nmol, A=None):
+    """Single-element :class:`Grouping` for ``n`` rows whose molecules are given by ``ordering[n]`` (upstream's
+    ``batch_indexes`` / ``indexes`` argument): row ``a`` becomes the ``k``-th row of molecule ``ordering[a]`` and gets the
+    private slot ``ordering[a] * A + k``.  Returns ``(grouping, A)`` with ``A`` = rows per molecule (at least the largest
+    count found).  Uses a few torch index operations and one host read of the largest count."""
+    dev = ordering.device
+    n = ordering.shape[0]
+    idx = ordering.long()
+    order = torch.argsort(idx, stable=True)
+    cnt = torch.bincount(idx, minlength=int(nmol))
+    first = torch.cumsum(cnt, 0) - cnt
+    rank = torch.empty_like(idx)
+    rank[order] = torch.arange(n, device=dev) - first[idx[order]]
+    most = int(cnt.max()) if n else 0
+    if A is None:
+        A = max(most, 1)
+    elif most > A:
+        raise RuntimeError("more rows of one molecule than atoms in the derivative tensor")
+    rows_cap = max((n + ROW_TILE - 1) // ROW_TILE * ROW_TILE, ROW_TILE)
+    slot = (idx * A + rank).to(torch.int32)
+    slot_of_row = torch.full((rows_cap,), -1, dtype=torch.int32, device=dev)
+    slot_of_row[:n] = slot
+    row_of_slot = torch.full((int(nmol) * A,), -1, dtype=torch.int32, device=dev)
+    row_of_slot[slot.long()] = torch.arange(n, dtype=torch.int32, device=dev)
+    group_start = torch.tensor([0, n], dtype=torch.int32, device=dev)
+    return Grouping(row_of_slot, slot_of_row, group_start, rows_cap, 1), A
+
+
+def pad_rows(t, rows_cap):
+    """``t`` with its first dimension zero-padded to ``rows_cap`` (the row capacity of a :class:`Grouping`)."""
+    if t.shape[0] == rows_cap:
+        return t.contiguous()
+    out = torch.zeros((rows_cap,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+    out[:t.shape[0]] = t
+    return out
+
+
 def group_by_element(Z, atom_counts, elements, n_atoms_upper=None):
     Z = Z.contiguous()
     nb, A = Z.shape
@@ -301,8 +338,20 @@ def _workspace(device, nbytes):
     return ws
 
 
+def pca_pair_pack(reductors):
+    """Split and tiled images of the projection matrices for both directions (``qmlb_pca_pair_pack``); pass the result
+    as ``pca_packed`` to the predict functions so that nothing is re-packed per call."""
+    nel, repsize, N = reductors.shape
+    lib = _lib.load()
+    nbytes = lib.qmlb_pca_pair_pack_bytes(nel, repsize, N)
+    packed = torch.empty(nbytes, dtype=torch.uint8, device=reductors.device)
+    check(lib.qmlb_pca_pair_pack(_p(reductors.contiguous(), torch.float32, 'reductors'), nel, repsize, N, _p(packed), nbytes,
+                                 _stream(reductors.device)), 'qmlb_pca_pair_pack')
+    return packed
+
+
 def sorf_predict(X, Z, atom_counts, fchl, elements, reductors, packed, S, T, sigma, cell=None, inv_cell=None,
-                 n_atoms_upper=None, fast_math=True, energy=None, grad_X=None):
+                 n_atoms_upper=None, fast_math=True, energy=None, grad_X=None, pca_packed=None):
     """Energies ``[nb]`` and ``dE/dX [nb,A,3]`` through ``qmlb_sorf_predict`` (one C call, no host sync)."""
     X, Z, atom_counts, nb, A = _batch(X, Z, atom_counts)
     cell, inv_cell = _cells(cell, inv_cell)
@@ -321,7 +370,7 @@ def sorf_predict(X, Z, atom_counts, fchl, elements, reductors, packed, S, T, sig
     check(lib.qmlb_sorf_predict(_p(X, torch.float32, 'coordinates'), _p(Z, torch.float32, 'charges'),
                                 _p(atom_counts, torch.int32, 'atom_counts'), nb, A, ctypes.byref(pc), _p(cell), _p(inv_cell),
                                 _p(elements.contiguous(), torch.float32, 'elements'), nel,
-                                _p(reductors.contiguous(), torch.float32, 'reductors'), N, _p(packed), int(S), int(T),
+                                _p(reductors.contiguous(), torch.float32, 'reductors'), _p(pca_packed), N, _p(packed), int(S), int(T),
                                 float(sigma), int(bool(fast_math)), upper, _p(ws), ws.numel(), _p(energy), _p(grad_X),
                                 _stream(X.device)), 'qmlb_sorf_predict')
     return energy, grad_X
@@ -368,7 +417,7 @@ def rff_energy_grad_tc(x, grouping, packed, nelements, fast_math=True):
 
 
 def rff_predict(X, Z, atom_counts, fchl, elements, reductors, W, b, alpha, cell=None, inv_cell=None, n_atoms_upper=None,
-                fast_math=True, energy=None, grad_X=None):
+                fast_math=True, energy=None, grad_X=None, pca_packed=None):
     """Energies ``[nb]`` and ``dE/dX [nb,A,3]`` of the RFF model through ``qmlb_rff_predict``."""
     X, Z, atom_counts, nb, A = _batch(X, Z, atom_counts)
     cell, inv_cell = _cells(cell, inv_cell)
@@ -387,7 +436,7 @@ def rff_predict(X, Z, atom_counts, fchl, elements, reductors, W, b, alpha, cell=
     check(lib.qmlb_rff_predict(_p(X, torch.float32, 'coordinates'), _p(Z, torch.float32, 'charges'),
                                _p(atom_counts, torch.int32, 'atom_counts'), nb, A, ctypes.byref(pc), _p(cell), _p(inv_cell),
                                _p(elements.contiguous(), torch.float32, 'elements'), nel,
-                               _p(reductors.contiguous(), torch.float32, 'reductors'), N,
+                               _p(reductors.contiguous(), torch.float32, 'reductors'), _p(pca_packed), N,
                                _p(W.contiguous(), torch.float32, 'W'), _p(b.contiguous(), torch.float32, 'b'),
                                _p(alpha.contiguous(), torch.float32, 'alpha'), D, int(bool(fast_math)), upper, _p(ws),
                                ws.numel(), _p(energy), _p(grad_X), _stream(X.device)), 'qmlb_rff_predict')
@@ -395,7 +444,7 @@ def rff_predict(X, Z, atom_counts, fchl, elements, reductors, W, b, alpha, cell=
 
 
 def rff_predict_packed(X, Z, atom_counts, fchl, elements, reductors, packed, cell=None, inv_cell=None, n_atoms_upper=None,
-                       fast_math=True, energy=None, grad_X=None):
+                       fast_math=True, energy=None, grad_X=None, pca_packed=None):
     """:func:`rff_predict` on parameters packed by :func:`rff_pack` (tensor-core feature stage, ``qmlb_rff_predict_packed``)."""
     X, Z, atom_counts, nb, A = _batch(X, Z, atom_counts)
     cell, inv_cell = _cells(cell, inv_cell)
@@ -413,7 +462,7 @@ def rff_predict_packed(X, Z, atom_counts, fchl, elements, reductors, packed, cel
     check(lib.qmlb_rff_predict_packed(_p(X, torch.float32, 'coordinates'), _p(Z, torch.float32, 'charges'),
                                       _p(atom_counts, torch.int32, 'atom_counts'), nb, A, ctypes.byref(pc), _p(cell),
                                       _p(inv_cell), _p(elements.contiguous(), torch.float32, 'elements'), nel,
-                                      _p(reductors.contiguous(), torch.float32, 'reductors'), N, _p(packed),
+                                      _p(reductors.contiguous(), torch.float32, 'reductors'), _p(pca_packed), N, _p(packed),
                                       int(bool(fast_math)), upper, _p(ws), ws.numel(), _p(energy), _p(grad_X),
                                       _stream(X.device)), 'qmlb_rff_predict_packed')
     return energy, grad_X
@@ -463,10 +512,13 @@ def sorf_train_features(x, dx, Dmat, bias, grouping, atom_counts, nb, A, sigma):
     return Z, G
 
 
-def normal_equations_accumulate(M, y, ZTZ, ZTy):
-    """``ZTZ += M^T M`` (upper triangle) and ``ZTy += M^T y`` in float64."""
+def normal_equations_accumulate(M, y, ZTZ, ZTy, library=False):
+    """``ZTZ += M^T M`` (upper triangle) and ``ZTy += M^T y`` in float64; ``library=True`` takes the cuBLAS route that is
+    kept for timing comparisons."""
     rows, F = M.shape
-    check(_lib.load().qmlb_normal_equations_accumulate(_p(M.contiguous(), torch.float64, 'M'), rows, F,
+    lib = _lib.load()
+    fn = lib.qmlb_normal_equations_accumulate_cublas if library else lib.qmlb_normal_equations_accumulate
+    check(fn(_p(M.contiguous(), torch.float64, 'M'), rows, F,
                                                        _p(None if y is None else y.contiguous(), torch.float64, 'y'),
                                                        _p(ZTZ, torch.float64, 'ZTZ'), _p(ZTy, torch.float64, 'ZTy'),
                                                        _stream(M.device)), 'qmlb_normal_equations_accumulate')
@@ -474,6 +526,54 @@ def normal_equations_accumulate(M, y, ZTZ, ZTy):
 
 def symmetrize_upper(ZTZ):
     check(_lib.load().qmlb_symmetrize_upper(_p(ZTZ, torch.float64, 'ZTZ'), ZTZ.shape[0], _stream(ZTZ.device)), 'qmlb_symmetrize_upper')
+
+
+def hadamard_features_accumulate(coeffs, bias, ordering, features):
+    """``features f64[nmol,F] += sqrt(2/F) cos(coeffs + bias)`` per row, row ``a`` going to molecule ``ordering[a]``."""
+    n, F = coeffs.shape
+    check(_lib.load().qmlb_hadamard_features_accumulate(_p(coeffs.contiguous(), torch.float32, 'sorf_matrix'),
+                                                        _p(bias.contiguous(), torch.float32, 'bias'),
+                                                        _p(ordering.contiguous(), torch.int32, 'ordering'), n, F,
+                                                        _p(features, torch.float64, 'features'), _stream(coeffs.device)),
+          'qmlb_hadamard_features_accumulate')
+
+
+def partial_feature_derivatives(coeffs, bias, out):
+    """``out f64[n,F] = sqrt(2/F) sin(coeffs + bias)``."""
+    n, F = coeffs.shape
+    check(_lib.load().qmlb_partial_feature_derivatives(_p(coeffs.contiguous(), torch.float32, 'sorf_matrix'),
+                                                       _p(bias.contiguous(), torch.float32, 'bias'), n, F,
+                                                       _p(out, torch.float64, 'sin_coeffs'), _stream(coeffs.device)),
+          'qmlb_partial_feature_derivatives')
+
+
+def featurization_derivative_accumulate(partial, normalisation, D, input_derivatives, ordering, feature_derivatives):
+    """``feature_derivatives f64[nmol,A,3,F] += normalisation * partial * (HD)^T input_derivatives`` (see the header)."""
+    T, S, N = D.shape
+    n, A = input_derivatives.shape[0], input_derivatives.shape[1]
+    check(_lib.load().qmlb_featurization_derivative_accumulate(
+        _p(partial.contiguous(), torch.float64, 'partial_feature_derivatives'), float(normalisation),
+        _p(D.contiguous(), torch.float32, 'scaling'), _p(input_derivatives.contiguous(), torch.float32, 'input_derivatives'),
+        _p(ordering.contiguous(), torch.int32, 'ordering'), n, A, N, S, T,
+        _p(feature_derivatives, torch.float64, 'feature_derivatives'), _stream(partial.device)),
+        'qmlb_featurization_derivative_accumulate')
+
+
+def pack_upper(ZTZ):
+    """Accumulated upper triangle of ``ZTZ f64[F,F]`` as a contiguous ``f64[F(F+1)/2]`` tensor."""
+    F = ZTZ.shape[0]
+    lib = _lib.load()
+    packed = torch.empty(lib.qmlb_packed_upper_elements(F), dtype=torch.float64, device=ZTZ.device)
+    check(lib.qmlb_pack_upper(_p(ZTZ, torch.float64, 'ZTZ'), F, _p(packed), _stream(ZTZ.device)), 'qmlb_pack_upper')
+    return packed
+
+
+def unpack_upper(packed, ZTZ):
+    """Inverse of :func:`pack_upper`; also mirrors the triangle, so ``ZTZ`` is symmetric afterwards."""
+    F = ZTZ.shape[0]
+    check(_lib.load().qmlb_unpack_upper(_p(packed, torch.float64, 'packed'), F, _p(ZTZ, torch.float64, 'ZTZ'),
+                                        _stream(ZTZ.device)), 'qmlb_unpack_upper')
+    return ZTZ
 
 
 def rff_train_features(x, dx, W, b, grouping, atom_counts, nb, A):

@@ -121,6 +121,84 @@ __global__ void assign_kernel(const float *__restrict__ Z, const int *__restrict
     }
 }
 
+// Small batches (at most SMALL_MOLS molecules): the three steps in ONE launch of one block.  Warp w owns the molecules
+// [32 w, 32 w + 32) exactly like block w of the three-kernel path, so both paths produce the same permutation; the
+// per-warp counts and their prefix stay in shared memory.  Saves two launches and the memset node, which is what a
+// 1,000-molecule prediction step is made of.
+constexpr int SMALL_MOLS = 1024;
+__global__ void __launch_bounds__(1024)
+group_small_kernel(const float *__restrict__ Z, const int *__restrict__ counts, const float *__restrict__ elements, int nel,
+                   int nb, int A, int *__restrict__ row_of_slot, int *__restrict__ slot_of_row, int *__restrict__ group_start,
+                   long rows_cap) {
+    __shared__ int cnt[MAX_ELEMENTS][32];      // [element][warp] counts, then exclusive prefix over the warps
+    __shared__ int gstart[MAX_ELEMENTS + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (long r = threadIdx.x; r < rows_cap; r += blockDim.x) slot_of_row[r] = -1;
+    const int m0 = warp * GROUP_MOLS, m1 = min(nb, m0 + GROUP_MOLS);
+    const long s0 = (long)m0 * A, s1 = (long)max(m1, m0) * A;
+    int local[MAX_ELEMENTS];
+    for (int e = 0; e < nel; ++e) local[e] = 0;
+    for (long s = s0 + lane; s < s1; s += 32) {
+        const int m = (int)(s / A), a = (int)(s % A);
+        if (a < counts[m]) {
+            const int e = element_of(Z[s], elements, nel);
+            for (int q = 0; q < nel; ++q) local[q] += (q == e);
+        }
+    }
+    for (int e = 0; e < nel; ++e) {
+        int v = local[e];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(QMLB_FULL_MASK, v, o);
+        if (lane == 0) cnt[e][warp] = v;
+    }
+    __syncthreads();
+    if (warp < nel) {                            // warp e scans element e over the 32 owning warps
+        const int v = cnt[warp][lane];
+        int inc = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(QMLB_FULL_MASK, inc, o);
+            if (lane >= o) inc += t;
+        }
+        cnt[warp][lane] = inc - v;
+        if (lane == 31) gstart[warp + 1] = (inc + QMLB_ROW_TILE - 1) / QMLB_ROW_TILE * QMLB_ROW_TILE;   // padded size
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int start = 0;
+        for (int e = 0; e < nel; ++e) {
+            const int padded = gstart[e + 1];
+            gstart[e] = start;
+            group_start[e] = start;
+            start += padded;
+        }
+        gstart[nel] = start;
+        group_start[nel] = start;
+    }
+    __syncthreads();
+    int next[MAX_ELEMENTS];
+    for (int e = 0; e < nel; ++e) next[e] = gstart[e] + cnt[e][warp];
+    for (long sb = s0; sb < s1; sb += 32) {
+        const long s = sb + lane;
+        int e = -1;
+        if (s < s1) {
+            const int m = (int)(s / A), a = (int)(s % A);
+            if (a < counts[m]) e = element_of(Z[s], elements, nel);
+        }
+        int row = -1;
+        for (int q = 0; q < nel; ++q) {
+            const unsigned msk = __ballot_sync(QMLB_FULL_MASK, e == q);
+            if (e == q) row = next[q] + __popc(msk & ((1u << lane) - 1u));
+            next[q] += __popc(msk);
+        }
+        if (s < s1) {
+            if (row >= rows_cap) row = QMLB_ROW_OVERFLOW;
+            row_of_slot[s] = row;
+            if (row >= 0) slot_of_row[row] = (int)s;
+        }
+    }
+}
+
 }  // namespace
 
 extern "C" size_t qmlb_rows_capacity(size_t n_atoms_upper, int nelements) {
@@ -143,6 +221,11 @@ extern "C" int qmlb_group_by_element(const float *Z, const int *atom_counts, con
     QMLB_REQUIRE((size_t)nb * A < (size_t)1 << 31, "qmlb_group_by_element: nb*A must fit in int32");
     QMLB_REQUIRE(rows_cap % QMLB_ROW_TILE == 0 && rows_cap < (size_t)1 << 31, "qmlb_group_by_element: bad rows_cap");
     cudaStream_t st = qmlb::as_stream(stream);
+    if (nb <= SMALL_MOLS) {
+        group_small_kernel<<<1, 1024, 0, st>>>(Z, atom_counts, elements, nelements, nb, A, row_of_slot, slot_of_row, group_start,
+                                               (long)rows_cap);
+        return qmlb::check_launch("qmlb_group_by_element");
+    }
     const int nblocks = (nb + GROUP_MOLS - 1) / GROUP_MOLS;
     int *block_counts = static_cast<int *>(scratch);
     // padding rows carry no atom: all bytes 0xFF = -1

@@ -1,9 +1,10 @@
 // Normal-equation accumulation  ZTZ += M^T M ,  ZTy += M^T y  in float64 for row blocks M = [Z; G] of one batch.
 //
 // Upstream: torch.matmul(Ztrain.T, Ztrain) and torch.matmul(Ztrain.T, targets) in build_Z_components
-// (models/kernel.py:172-192).  This is a plain dense contraction, so it goes to the library: cuBLAS DSYRK computes
-// only one triangle (half the flops of the upstream DGEMM), DGEMV the right-hand side; a small kernel mirrors the
-// triangle before the solve.  One cuBLAS handle per device, bound to the caller's stream on every call.
+// (models/kernel.py:172-192).  qmlb_normal_equations_accumulate runs the in-tree kernels of syrk_f64.cu;
+// qmlb_normal_equations_accumulate_cublas is the same update through cuBLAS DSYRK + DGEMV, kept as the library
+// yardstick the in-tree kernel is timed against (one handle per device, bound to the caller's stream on every call).
+// Small kernels mirror the triangle before the solve and pack / unpack it for the exchange between ranks.
 #include <cublas_v2.h>
 
 #include <mutex>
@@ -40,10 +41,48 @@ __global__ void mirror_kernel(double *C, int F) {
     if (i < F && j < F && j > i) C[(size_t)j * F + i] = C[(size_t)i * F + j];
 }
 
+// Row i of the packed triangle starts at i*F - i*(i-1)/2 and holds columns i..F-1: both sides of the copy are contiguous.
+__device__ __forceinline__ size_t packed_row_start(size_t i, size_t F) { return i * F - (i * (i - 1)) / 2; }
+
+template <bool PACK>
+__global__ void triangle_copy_kernel(double *C, double *packed, int F) {
+    const size_t i = blockIdx.y;
+    const size_t j = i + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= (size_t)F) return;
+    const size_t a = i * (size_t)F + j, b = packed_row_start(i, F) + (j - i);
+    if (PACK) packed[b] = C[a];
+    else C[a] = packed[b];
+}
+
 }  // namespace
+
+extern "C" size_t qmlb_packed_upper_elements(int F) { return F > 0 ? (size_t)F * ((size_t)F + 1) / 2 : 0; }
+
+extern "C" int qmlb_pack_upper(const double *ZTZ, int F, double *packed, qmlb_stream_t stream) {
+    QMLB_REQUIRE(ZTZ && packed && F > 0 && F <= 65535, "qmlb_pack_upper: bad arguments");
+    dim3 block(256), grid((F + 255) / 256, F);
+    triangle_copy_kernel<true><<<grid, block, 0, qmlb::as_stream(stream)>>>(const_cast<double *>(ZTZ), packed, F);
+    return qmlb::check_launch("qmlb_pack_upper");
+}
+
+extern "C" int qmlb_unpack_upper(const double *packed, int F, double *ZTZ, qmlb_stream_t stream) {
+    QMLB_REQUIRE(ZTZ && packed && F > 0 && F <= 65535, "qmlb_unpack_upper: bad arguments");
+    dim3 block(256), grid((F + 255) / 256, F);
+    triangle_copy_kernel<false><<<grid, block, 0, qmlb::as_stream(stream)>>>(ZTZ, const_cast<double *>(packed), F);
+    if (int rc = qmlb::check_launch("qmlb_unpack_upper")) return rc;
+    return qmlb_symmetrize_upper(ZTZ, F, stream);
+}
 
 extern "C" int qmlb_normal_equations_accumulate(const double *M, int rows, int F, const double *y, double *ZTZ,
                                                 double *ZTy, qmlb_stream_t stream) {
+    QMLB_REQUIRE(M && ZTZ, "qmlb_normal_equations_accumulate: null tensor");
+    QMLB_REQUIRE((y == nullptr) == (ZTy == nullptr), "qmlb_normal_equations_accumulate: y and ZTy go together");
+    if (int rc = qmlb_syrk_f64(M, rows, F, ZTZ, stream)) return rc;
+    return y ? qmlb_gemv_t_f64(M, rows, F, y, ZTy, stream) : QMLB_OK;
+}
+
+extern "C" int qmlb_normal_equations_accumulate_cublas(const double *M, int rows, int F, const double *y, double *ZTZ,
+                                                       double *ZTy, qmlb_stream_t stream) {
     QMLB_REQUIRE(M && ZTZ, "qmlb_normal_equations_accumulate: null tensor");
     QMLB_REQUIRE((y == nullptr) == (ZTy == nullptr), "qmlb_normal_equations_accumulate: y and ZTy go together");
     QMLB_REQUIRE(rows >= 0 && F > 0, "qmlb_normal_equations_accumulate: bad sizes");

@@ -14,10 +14,11 @@
 //     issues the MMAs, one warp issues the copies; two stages of (A 32 KB + B up to 64 KB).
 // The tensor core adds into its fp32 accumulator with truncation towards zero, which biases long accumulations.  The
 // small cross terms (hi*lo, lo*hi) therefore have their own accumulator columns, and the accumulators are folded into
-// fp32 registers every `group_chunks` chunks (3 = 96 k = 12 truncating adds of hi*hi terms for the projection, whose
-// result feeds cos(); 8 for the transposed product, K = npcas <= 256, which feeds only the force chain rule).  Folding
-// every chunk into a second accumulator buffer instead (so that it overlaps the next MMAs) was slower: the eight
-// worker warps then fold four times as often and become the bottleneck (c1 projection 0.42 ms against 0.35 ms).
+// fp32 registers every `group_chunks` chunks: 1 (32 k, 4 truncating adds of hi*hi terms) for the projection, whose
+// result feeds cos() -- measured on a 21-atom model with weights of magnitude 10^3, the projected rows are then
+// 3.0e-7 from float64 (relative to their maximum; an fp32 FFMA loop: 4.4e-7; folding every 3 chunks: 1.25e-6, which
+// tripled the force error of the whole chain) for 0.4 % of the step time -- and 8 for the transposed product,
+// K = npcas <= 256, which feeds only the force chain rule and is not limited by the truncation.
 // Tensor memory: hi*hi columns [0, NT), cross-term columns [256, 256 + NT); all 512 columns are allocated.
 // Every wait is bounded; a block that times out skips its stores, waits (bounded) for copies and MMAs in flight,
 // frees its tensor memory and counts the event (qmlb_tc_timeouts).
@@ -411,8 +412,8 @@ extern "C" int qmlb_pca_project_packed(const float *in, const void *packed, cons
     const Tiling t = make_tiling(repsize, npcas, transpose);
     const size_t smem = (size_t)NSTAGES * (2 * A_HALF + t.chunk_bytes) + 128;
     if (int rc = qmlb::ensure_smem(pca_tc2_kernel, smem, "qmlb_pca_project_packed")) return rc;
-    // projection: fold every 3 chunks (96 k); transposed product (K = npcas): fold once per 8 chunks
-    const int group_chunks = transpose ? 8 : 3;
+    // projection: fold every chunk (32 k); transposed product (K = npcas): fold once per 8 chunks
+    const int group_chunks = transpose ? 8 : 1;
     dim3 grid((unsigned)(rows_cap / BM), (unsigned)t.ntiles);
     static std::atomic<unsigned> launches{0};
     const unsigned seq = ++launches;   // never 0, the initial value of the device-side marker

@@ -319,7 +319,7 @@ class SorfEnergyFn : public torch::autograd::Function<SorfEnergyFn> {
         if (b.nb > 0)
         check(qmlb_sorf_predict(b.X.data_ptr<float>(), b.Z.data_ptr<float>(), b.counts.data_ptr<int>(), b.nb, b.A, &f.p,
                                 cell_ptr(b.cell), cell_ptr(b.inv_cell), el.data_ptr<float>(), nel, red.data_ptr<float>(),
-                                npcas, pk.data_ptr<float>(), (int)nstacks, (int)ntransforms, (float)sigma, fast_math ? 1 : 0,
+                                nullptr, npcas, pk.data_ptr<float>(), (int)nstacks, (int)ntransforms, (float)sigma, fast_math ? 1 : 0,
                                 upper, wp, bytes, E.data_ptr<float>(), gX.data_ptr<float>(), current_stream()),
               "sorf_energy");
         ctx->save_for_backward({gX});
@@ -385,7 +385,7 @@ class RffEnergyFn : public torch::autograd::Function<RffEnergyFn> {
         if (bt.nb > 0)
         check(qmlb_rff_predict_packed(bt.X.data_ptr<float>(), bt.Z.data_ptr<float>(), bt.counts.data_ptr<int>(), bt.nb, bt.A,
                                       &f.p, cell_ptr(bt.cell), cell_ptr(bt.inv_cell), el.data_ptr<float>(), nel,
-                                      red.data_ptr<float>(), npcas, packed.data_ptr<uint8_t>(), fast_math ? 1 : 0, upper, wp,
+                                      red.data_ptr<float>(), nullptr, npcas, packed.data_ptr<uint8_t>(), fast_math ? 1 : 0, upper, wp,
                                       bytes, E.data_ptr<float>(), gX.data_ptr<float>(), current_stream()),
               "rff_energy");
         ctx->save_for_backward({gX});

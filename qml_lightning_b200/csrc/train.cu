@@ -13,30 +13,9 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "fwht.cuh"
 
 namespace {
-
-template <int E>
-__device__ __forceinline__ void warp_fwht(float (&u)[E], int lane) {
-#pragma unroll
-    for (int h = 1; h < E; h <<= 1)
-#pragma unroll
-        for (int i = 0; i < E; ++i)
-            if ((i & h) == 0) {
-                const float a = u[i], b = u[i | h];
-                u[i] = a + b;
-                u[i | h] = a - b;
-            }
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const float sgn = (lane & o) ? -1.0f : 1.0f;
-#pragma unroll
-        for (int i = 0; i < E; ++i) {
-            const float other = __shfl_xor_sync(QMLB_FULL_MASK, u[i], o);
-            u[i] = fmaf(sgn, u[i], other);
-        }
-    }
-}
 
 __device__ __forceinline__ int element_of_row(long row, const int *group_start, int nel) {
     int e = 0;

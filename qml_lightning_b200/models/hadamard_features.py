@@ -131,7 +131,8 @@ class HadamardFeaturesModel(BaseKernel, torch.nn.Module):
             # the fused operator already holds dE/dX; calling the C entry point directly skips the autograd graph
             energies, grad = cabi.sorf_predict(coordinates, charges, natom_counts, self.rep.kernel_params(dev), self.species,
                                                self.reductors, self.packed, self.nstacks, self.ntransforms_int, self.sigma,
-                                               cells, inv_cells, n_atoms_upper=atomIDs.shape[0], fast_math=self.fast_math)
+                                               cells, inv_cells, n_atoms_upper=atomIDs.shape[0], fast_math=self.fast_math,
+                                               pca_packed=self.pca_packed())
             result = (energies, -grad)
         else:
             with torch.no_grad():

@@ -165,6 +165,17 @@ class BaseKernel():
     def _parameters_changed(self):
         """Hook for subclasses that cache derived parameter buffers."""
 
+    def pca_packed(self):
+        """Split and tiled images of ``self.reductors`` for the tensor-core projection, rebuilt only when the tensor
+        was replaced or written to since the last call (``get_reductors``, direct assignment, in-place edits)."""
+        from .. import cabi
+        red = self.reductors
+        key = (red.data_ptr(), red._version, tuple(red.shape), red.device)
+        if getattr(self, '_pca_packed_key', None) != key:
+            self._pca_packed = cabi.pca_pair_pack(red.contiguous().float())
+            self._pca_packed_key = key
+        return self._pca_packed
+
     # ---- training --------------------------------------------------------------------------------------------
     def training_rows(self, data, with_forces):
         """``(Z f64[zbatch,F], G f64[zbatch,A,3,F] | None)`` for one formatted batch; implemented by the models."""
@@ -186,30 +197,9 @@ class BaseKernel():
         if n == 0:
             return
         with_grad = grad is not None and derivative_matrix is not None
-        idx = indexes.to(dev).long()
-        # position of every row among the rows of its molecule -> a private (molecule, position) slot
-        order = torch.argsort(idx, stable=True)
-        cnt = torch.bincount(idx, minlength=nb)
-        first = torch.cumsum(cnt, 0) - cnt
-        rank = torch.empty_like(idx)
-        rank[order] = torch.arange(n, device=dev) - first[idx[order]]
-        A = int(grad.shape[1]) if with_grad else int(cnt.max())
-        if int(cnt.max()) > A:
-            raise RuntimeError("calculate_features: more rows of one molecule than atoms in grad")
-        rows_cap = (n + cabi.ROW_TILE - 1) // cabi.ROW_TILE * cabi.ROW_TILE
-        slot = (idx * A + rank).to(torch.int32)
-        slot_of_row = torch.full((rows_cap,), -1, dtype=torch.int32, device=dev)
-        slot_of_row[:n] = slot
-        row_of_slot = torch.full((nb * A,), -1, dtype=torch.int32, device=dev)
-        row_of_slot[slot.long()] = torch.arange(n, dtype=torch.int32, device=dev)
-        group_start = torch.tensor([0, n], dtype=torch.int32, device=dev)
-        g = cabi.Grouping(row_of_slot, slot_of_row, group_start, rows_cap, 1)
-        x = torch.zeros(rows_cap, rep.shape[1], dtype=torch.float32, device=dev)
-        x[:n] = rep
-        dx = None
-        if with_grad:
-            dx = torch.zeros(rows_cap, A, 3, rep.shape[1], dtype=torch.float32, device=dev)
-            dx[:n] = grad
+        g, A = cabi.grouping_from_ordering(indexes.to(dev), nb, int(grad.shape[1]) if with_grad else None)
+        x = cabi.pad_rows(rep.float(), g.rows_cap)
+        dx = cabi.pad_rows(grad.float(), g.rows_cap) if with_grad else None
         counts = torch.full((nb,), A, dtype=torch.int32, device=dev)
         Z, G = self._element_features(x, dx, int(self.element2index[int(element)]), g, counts, nb, A)
         feature_matrix += Z
@@ -218,12 +208,10 @@ class BaseKernel():
 
     @staticmethod
     def allreduce_normal_equations(ZTZ, ZtrainY):
-        """Sum the per-rank partial normal equations in place (no-op without an initialised process group)."""
-        import torch.distributed as dist
-        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
-            dist.all_reduce(ZTZ, op=dist.ReduceOp.SUM)
-            dist.all_reduce(ZtrainY, op=dist.ReduceOp.SUM)
-        return ZTZ, ZtrainY
+        """Sum the per-rank partial normal equations in place (packed upper triangle, one all-reduce) and mirror the
+        triangle; without an initialised process group only the mirroring happens."""
+        from ..utils.distributed import allreduce_normal_equations
+        return allreduce_normal_equations(ZTZ, ZtrainY)
 
     def build_Z_components(self, X, Q, E=None, F=None, cells=None, inv_cells=None, print_info=True, cpu_solve=False, ntiles=1,
                            use_specialized_matmul=False, distributed=False):
@@ -231,9 +219,9 @@ class BaseKernel():
 
         Rows per molecule: one energy row and, with forces, ``3 * max_atoms`` force rows (``G = -dZ/dr``), targets
         ``cat(E, F.flatten())`` -- the construction of upstream build_Z_components (kernel.py:46-217).  Only the upper
-        triangle is accumulated (DSYRK) and mirrored once at the end.  With ``distributed=True`` every rank of the
+        triangle is accumulated and mirrored once at the end.  With ``distributed=True`` every rank of the
         initialised process group takes a contiguous, atom-balanced share of the molecules and the partial sums are
-        combined with one all-reduce.  ``ntiles`` and ``use_specialized_matmul`` are accepted for signature
+        combined with one all-reduce of the packed triangle.  ``ntiles`` and ``use_specialized_matmul`` are accepted for signature
         compatibility: the full matrix is kept on the device.
         """
         from .. import cabi
@@ -264,9 +252,10 @@ class BaseKernel():
                 targets = torch.cat((data['energies'], data['forces'].flatten()))
             rows = Ztrain if Gtrain is None else torch.cat((Ztrain, Gtrain.reshape(-1, nf)), dim=0)
             cabi.normal_equations_accumulate(rows, targets.contiguous(), ZTZ, ZtrainY)
-        cabi.symmetrize_upper(ZTZ)
         if distributed:
-            self.allreduce_normal_equations(ZTZ, ZtrainY)
+            self.allreduce_normal_equations(ZTZ, ZtrainY)       # packed triangle over the ranks, mirrored afterwards
+        else:
+            cabi.symmetrize_upper(ZTZ)
         if cpu_solve:
             ZTZ = ZTZ.cpu()
         return ZTZ, ZtrainY
@@ -277,7 +266,12 @@ class BaseKernel():
         definite, so a Cholesky factorisation replaces upstream's LU; LU is the fallback if the factorisation fails."""
         ZTZ, ZtrainY = self.build_Z_components(X, Q, E, F, cells, inv_cells, print_info, cpu_solve, ntiles,
                                                use_specialized_matmul, distributed)
-        alpha = self.solve_normal_equations(ZTZ, ZtrainY)
+        if distributed:
+            # one factorisation on rank 0, the weights (8 bytes per feature) broadcast to the others
+            from ..utils.distributed import solve_on_rank0_and_broadcast
+            alpha = solve_on_rank0_and_broadcast(self.solve_normal_equations, ZTZ, ZtrainY, self.nfeatures(), self.rep.device)
+        else:
+            alpha = self.solve_normal_equations(ZTZ, ZtrainY)
         self.alpha = alpha.to(self.rep.device)
         self.is_trained = True
         self._parameters_changed()

@@ -88,7 +88,8 @@ class RandomFourrierFeaturesModel(BaseKernel, torch.nn.Module):
         dev = coordinates.device
         energies, grad = cabi.rff_predict_packed(coordinates, charges, natom_counts, self.rep.kernel_params(dev), self.species,
                                                  self.reductors, self.packed, zcells, zinv_cells,
-                                                 n_atoms_upper=atomIDs.shape[0], fast_math=self.fast_math)
+                                                 n_atoms_upper=atomIDs.shape[0], fast_math=self.fast_math,
+                                                 pca_packed=self.pca_packed())
         if print_info:
             torch.cuda.synchronize()
             print("prediction for", coordinates.shape[0], "molecules")

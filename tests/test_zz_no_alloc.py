@@ -37,7 +37,8 @@ def _noalloc(Z, counts, elements):
 
 def test_noalloc_grouping_matches_regular_entry_point_twice_in_a_row():
     from qml_lightning_b200 import cabi
-    batches = [H.batch_mixed(300, seed=21), H.batch_c0(500, seed=22)]     # second call sees the first call's leftovers
+    # more than 1,024 molecules each: smaller batches are grouped by a single-block kernel that needs no scratch at all
+    batches = [H.batch_mixed(1500, seed=21), H.batch_c0(2100, seed=22)]   # second call sees the first call's leftovers
     for X, Z, c, species in batches:
         Zd, cd = Z.to(DEV).contiguous(), c.to(DEV).contiguous()
         el = torch.tensor(species, dtype=torch.float32, device=DEV)

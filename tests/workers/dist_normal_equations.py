@@ -5,7 +5,8 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspa
 import torch.distributed as dist
 rank = int(os.environ['RANK']); world = int(os.environ['WORLD_SIZE']); local = int(os.environ['LOCAL_RANK'])
 torch.cuda.set_device(local)
-dist.init_process_group('nccl', device_id=torch.device('cuda', local))
+from qml_lightning_b200.utils.distributed import init_process_group
+init_process_group('nccl', timeout_s=120, device=torch.device('cuda', local))
 from tests import helpers as H
 from tests.test_gpu_models import build_model
 import tests.test_gpu_models as tm
@@ -19,5 +20,11 @@ A1, y1 = m.build_Z_components(Xl, Zl, E, Fl, print_info=False, distributed=False
 A2, y2 = m.build_Z_components(Xl, Zl, E, Fl, print_info=False, distributed=True)
 err = float((A1 - A2).abs().max() / A1.abs().max()); erry = float((y1 - y2).abs().max() / y1.abs().max())
 print(f'rank {rank}: sharded vs full ZTZ rel err {err:.3e}, ZTy {erry:.3e}')
-assert err < 1e-6 and erry < 1e-6
+assert err < 1e-12 and erry < 1e-12
+assert float((A2 - A2.T).abs().max()) == 0.0
+# train(distributed=True): rank 0 solves, every rank receives the same weights; equal to the single-rank solve
+m.train(Xl, Zl, E, Fl, print_info=False, distributed=True)
+a_dist = m.alpha.clone()
+m.train(Xl, Zl, E, Fl, print_info=False, distributed=False)
+assert float((a_dist - m.alpha).abs().max()) <= 1e-8 * float(m.alpha.abs().max())
 dist.destroy_process_group()
