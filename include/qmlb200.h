@@ -328,13 +328,14 @@ int qmlb_featurization_derivative_accumulate(const double *partial_derivatives, 
 /* RFF training features of one batch: random_fourrier_features_kernel / _derivative
  * (cuda/random_features_kernel.cu:5-94) via get_rff / get_rff_derivatives (cuda/random_features.cpp:11-33), as
  * driven by RandomFourrierFeaturesModel.calculate_features (models/random_features.py:60-67), for all elements
- * at once.  x f32[rows_cap,K], dx f32[rows_cap,A,3,K] element-grouped; W f32[nel,K,D], b f32[nel,D].
- * Zout f64[nb,D], G f64[nb,A,3,D] (= -dZ/dr) overwritten.  arg_scratch: rows_cap*D floats; t_scratch:
- * rows_cap*A*3*D floats (NULL together with dx and G for energy-only training). */
+ * at once and with upstream's arithmetic: float32 inputs, float64 products, sums and sin/cos (upstream passes
+ * W.double(), b.double()).  x f32[rows_cap,K], dx f32[rows_cap,A,3,K] element-grouped; W f32[nel,K,D], b f32[nel,D].
+ * Zout f64[nb,D] and G f64[nb,A,3,D] (= -dZ/dr) are overwritten, every element written once (dx and G may both be
+ * NULL for energy-only training).  One fused kernel (float64 tensor-core products with the sin/cos scaling and the
+ * per-molecule sum in registers); no scratch memory.  K must be a multiple of 4. */
 int qmlb_rff_train_features(const float *x, const float *dx, const float *W, const float *b, const int *group_start,
                             const int *slot_of_row, const int *row_of_slot, const int *atom_counts, int nelements, int nb,
-                            int A, size_t rows_cap, int K, int D, double *Zout, double *G, float *arg_scratch,
-                            float *t_scratch, qmlb_stream_t stream);
+                            int A, size_t rows_cap, int K, int D, double *Zout, double *G, qmlb_stream_t stream);
 
 /* ZTZ += M^T M (row-major UPPER triangle only) and ZTy += M^T y for a row block M f64[rows,F]:
  * torch.matmul(Ztrain.T, Ztrain) / torch.matmul(Ztrain.T, targets) in build_Z_components (models/kernel.py:172-192).
@@ -347,6 +348,14 @@ int qmlb_normal_equations_accumulate(const double *M, int rows, int F, const dou
 int qmlb_normal_equations_accumulate_cublas(const double *M, int rows, int F, const double *y, double *ZTZ, double *ZTy,
                                             qmlb_stream_t stream);
 int qmlb_syrk_f64(const double *M, int rows, int F, double *ZTZ, qmlb_stream_t stream);
+
+/* C f64[Fi,Fj] += P^T Q for P f64[rows,Fi], Q f64[rows,Fj] (all row-major), every entry of C: the product behind
+ * matmul_and_reduce (cuda/utils_cuda.cpp:26-33, kernel cuda/utils_kernel.cu:70-129: C += A B with A = P^T, B = Q),
+ * which upstream selects with use_specialized_matmul (models/kernel.py:176-188) and feeds with float32 copies of the
+ * rows.  Here the float32-rounded rows are promoted and multiplied on the float64 tensor-core path (the same kernel
+ * as qmlb_syrk_f64), so every product is exact and the sums carry float64 rounding only: closer to the exact
+ * product than upstream's compensated float32 sum. */
+int qmlb_gemm_tn_f64(const double *P, const double *Q, int rows, int Fi, int Fj, double *C, qmlb_stream_t stream);
 int qmlb_gemv_t_f64(const double *M, int rows, int F, const double *y, double *ZTy, qmlb_stream_t stream);
 int qmlb_symmetrize_upper(double *ZTZ, int F, qmlb_stream_t stream);
 

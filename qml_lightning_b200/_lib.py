@@ -71,7 +71,7 @@ SIGNATURES = {
                                          c_int, c_int, c_size_t, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p,
                                          c_void_p]),
     'qmlb_rff_train_features': (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                        c_int, c_size_t, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+                                        c_int, c_size_t, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     'qmlb_hadamard_features_accumulate': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     'qmlb_partial_feature_derivatives': (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     'qmlb_featurization_derivative_accumulate': (c_int, [c_void_p, ctypes.c_double, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -79,6 +79,7 @@ SIGNATURES = {
     'qmlb_normal_equations_accumulate': (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     'qmlb_normal_equations_accumulate_cublas': (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     'qmlb_syrk_f64': (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    'qmlb_gemm_tn_f64': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     'qmlb_gemv_t_f64': (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     'qmlb_symmetrize_upper': (c_int, [c_void_p, c_int, c_void_p]),
     'qmlb_packed_upper_elements': (c_size_t, [c_int]),

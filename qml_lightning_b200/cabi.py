@@ -524,6 +524,13 @@ def normal_equations_accumulate(M, y, ZTZ, ZTy, library=False):
                                                        _stream(M.device)), 'qmlb_normal_equations_accumulate')
 
 
+def gemv_t(M, y, ZTy):
+    """``ZTy += M^T y`` in float64 (``qmlb_gemv_t_f64``)."""
+    rows, F = M.shape
+    check(_lib.load().qmlb_gemv_t_f64(_p(M.contiguous(), torch.float64, 'M'), rows, F, _p(y.contiguous(), torch.float64, 'y'),
+                                      _p(ZTy, torch.float64, 'ZTy'), _stream(M.device)), 'qmlb_gemv_t_f64')
+
+
 def symmetrize_upper(ZTZ):
     check(_lib.load().qmlb_symmetrize_upper(_p(ZTZ, torch.float64, 'ZTZ'), ZTZ.shape[0], _stream(ZTZ.device)), 'qmlb_symmetrize_upper')
 
@@ -559,6 +566,24 @@ def featurization_derivative_accumulate(partial, normalisation, D, input_derivat
         'qmlb_featurization_derivative_accumulate')
 
 
+def matmul_and_reduce(A, B, C):
+    """``C f64[M,N] += A[M,K] @ B[K,N]`` in place (upstream ``utils_gpu.matmul_and_reduce``): the operands are taken at
+    float32 precision, as upstream passes them, promoted, and multiplied by ``qmlb_gemm_tn_f64``."""
+    if not (A.is_cuda and B.is_cuda and C.is_cuda):
+        raise RuntimeError("matmul_and_reduce: tensors must be CUDA tensors")
+    if C.dtype != torch.float64 or not C.is_contiguous():
+        raise RuntimeError("matmul_and_reduce: C must be a contiguous float64 tensor")
+    M, K = A.shape
+    K2, N = B.shape
+    if K2 != K or tuple(C.shape) != (M, N):
+        raise RuntimeError("matmul_and_reduce: shape mismatch")
+    P = A.float().T.contiguous().double()          # [K, M]; no copy of the float32 data when A is a transposed view
+    Q = P if (B.data_ptr() == A.data_ptr() and B.shape == P.shape and B.is_contiguous() and A.stride() == (1, M)) \
+        else B.float().contiguous().double()
+    check(_lib.load().qmlb_gemm_tn_f64(_p(P, torch.float64, 'A'), _p(Q, torch.float64, 'B'), K, M, N, _p(C), _stream(C.device)),
+          'qmlb_gemm_tn_f64')
+
+
 def pack_upper(ZTZ):
     """Accumulated upper triangle of ``ZTZ f64[F,F]`` as a contiguous ``f64[F(F+1)/2]`` tensor."""
     F = ZTZ.shape[0]
@@ -582,13 +607,11 @@ def rff_train_features(x, dx, W, b, grouping, atom_counts, nb, A):
     dev = x.device
     Z = torch.empty(nb, D, dtype=torch.float64, device=dev)
     G = torch.empty(nb, A, 3, D, dtype=torch.float64, device=dev) if dx is not None else None
-    arg = torch.empty(grouping.rows_cap, D, dtype=torch.float32, device=dev)
-    T = torch.empty(grouping.rows_cap, A, 3, D, dtype=torch.float32, device=dev) if dx is not None else None
     check(_lib.load().qmlb_rff_train_features(_p(x, torch.float32, 'x'), _p(dx, torch.float32, 'dx'), _p(W.contiguous(), torch.float32, 'W'),
                                               _p(b.contiguous(), torch.float32, 'b'), _p(grouping.group_start),
                                               _p(grouping.slot_of_row), _p(grouping.row_of_slot),
                                               _p(atom_counts.contiguous(), torch.int32, 'atom_counts'), nel, nb, A,
-                                              grouping.rows_cap, K, D, _p(Z), _p(G), _p(arg), _p(T), _stream(dev)),
+                                              grouping.rows_cap, K, D, _p(Z), _p(G), _stream(dev)),
           'qmlb_rff_train_features')
     return Z, G
 

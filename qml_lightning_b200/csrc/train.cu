@@ -161,81 +161,3 @@ extern "C" int qmlb_sorf_train_features(const float *x, const float *dx, const f
     }
 #undef QMLB_TRAIN
 }
-
-// ---- RFF training rows ------------------------------------------------------------------------------------------
-// Upstream: random_fourrier_features_kernel / _derivative (cuda/random_features_kernel.cu:5-94) via get_rff /
-// get_rff_derivatives (cuda/random_features.cpp:11-33), one serial dot product per (atom, feature) and per
-// (atom, derivative atom, axis, feature).  Here the two dense products  arg = x W_e  and  T = dx W_e  are grouped
-// GEMMs (the projection kernel with W_e in the role of the projection matrix); two elementwise kernels finish:
-//   Z[mol, f] += sqrt(2/D) cos(arg + b)  (float64 atomics) ,  sinc = sqrt(2/D) sin(arg + b) ,
-//   G[mol, j, x, f] = sum_i sinc[row_i, f] * T[row_i, j, x, f]   (every element written once).
-namespace {
-
-__global__ void __launch_bounds__(256)
-rff_train_features_kernel(float *__restrict__ arg, const float *__restrict__ b, const int *__restrict__ group_start,
-                          const int *__restrict__ slot_of_row, int nel, int A, int D, float normf, double *__restrict__ Zout) {
-    const long row = blockIdx.y;
-    if (row >= group_start[nel]) return;
-    const int slot = slot_of_row[row];
-    if (slot < 0) return;
-    const int el = element_of_row(row, group_start, nel);
-    const int mol = slot / A;
-    for (int f = blockIdx.x * blockDim.x + threadIdx.x; f < D; f += gridDim.x * blockDim.x) {
-        float sn, cs;
-        sincosf(arg[(size_t)row * D + f] + b[(size_t)el * D + f], &sn, &cs);
-        atomicAdd(Zout + (size_t)mol * D + f, (double)(cs * normf));
-        arg[(size_t)row * D + f] = sn * normf;
-    }
-}
-
-__global__ void __launch_bounds__(256)
-rff_train_reduce_kernel(const float *__restrict__ T, const float *__restrict__ sinc, const int *__restrict__ row_of_slot,
-                        const int *__restrict__ atom_counts, int nb, int A, int D, double *__restrict__ G) {
-    // blockIdx.y = (mol, j, axis); threads over features
-    const int xd = blockIdx.y % 3;
-    const int j = (blockIdx.y / 3) % A;
-    const int mol = blockIdx.y / (3 * A);
-    int natoms = atom_counts[mol];
-    natoms = natoms > A ? A : natoms;
-    for (int f = blockIdx.x * blockDim.x + threadIdx.x; f < D; f += gridDim.x * blockDim.x) {
-        float acc = 0.f;
-        if (j < natoms) {
-            for (int ia = 0; ia < natoms; ++ia) {
-                const int row = row_of_slot[(size_t)mol * A + ia];
-                if (row < 0) continue;
-                acc = fmaf(sinc[(size_t)row * D + f], T[(((size_t)row * A + j) * 3 + xd) * D + f], acc);
-            }
-        }
-        G[(((size_t)mol * A + j) * 3 + xd) * D + f] = (double)acc;
-    }
-}
-
-}  // namespace
-
-extern "C" int qmlb_rff_train_features(const float *x, const float *dx, const float *W, const float *b,
-                                       const int *group_start, const int *slot_of_row, const int *row_of_slot,
-                                       const int *atom_counts, int nelements, int nb, int A, size_t rows_cap, int K, int D,
-                                       double *Zout, double *G, float *arg_scratch, float *t_scratch, qmlb_stream_t stream) {
-    QMLB_REQUIRE(x && W && b && group_start && slot_of_row && row_of_slot && atom_counts && Zout && arg_scratch,
-                 "qmlb_rff_train_features: null tensor");
-    QMLB_REQUIRE((dx == nullptr) == (G == nullptr) && (dx == nullptr) == (t_scratch == nullptr),
-                 "qmlb_rff_train_features: dx, G and t_scratch go together");
-    QMLB_REQUIRE(nelements > 0 && nb > 0 && A > 0 && K > 0 && D > 0, "qmlb_rff_train_features: bad sizes");
-    QMLB_REQUIRE(rows_cap < 65536 && (size_t)nb * A * 3 < 65536, "qmlb_rff_train_features: at most 65535 rows and nb*A*3 per call");
-    cudaStream_t st = qmlb::as_stream(stream);
-    if (cudaMemsetAsync(Zout, 0, sizeof(double) * (size_t)nb * D, st) != cudaSuccess)
-        return qmlb::check_launch("qmlb_rff_train_features(memset)");
-    // arg = x W_e : the grouped projection GEMM with (repsize, npcas) := (K, D)
-    if (int rc = qmlb_pca_project(x, W, group_start, nelements, rows_cap, K, D, 0, arg_scratch, stream)) return rc;
-    const float normf = (float)sqrt(2.0 / (double)D);
-    dim3 g1((unsigned)((D + 255) / 256), (unsigned)rows_cap);
-    rff_train_features_kernel<<<g1, 256, 0, st>>>(arg_scratch, b, group_start, slot_of_row, nelements, A, D, normf, Zout);
-    if (int rc = qmlb::check_launch("qmlb_rff_train_features")) return rc;
-    if (dx) {
-        if (int rc = qmlb_pca_project_jacobian(dx, W, group_start, nelements, rows_cap, 3 * A, K, D, t_scratch, stream)) return rc;
-        dim3 g2((unsigned)((D + 255) / 256), (unsigned)(nb * A * 3));
-        rff_train_reduce_kernel<<<g2, 256, 0, st>>>(t_scratch, arg_scratch, row_of_slot, atom_counts, nb, A, D, G);
-        return qmlb::check_launch("qmlb_rff_train_features(derivative)");
-    }
-    return QMLB_OK;
-}

@@ -221,8 +221,9 @@ class BaseKernel():
         ``cat(E, F.flatten())`` -- the construction of upstream build_Z_components (kernel.py:46-217).  Only the upper
         triangle is accumulated and mirrored once at the end.  With ``distributed=True`` every rank of the
         initialised process group takes a contiguous, atom-balanced share of the molecules and the partial sums are
-        combined with one all-reduce of the packed triangle.  ``ntiles`` and ``use_specialized_matmul`` are accepted for signature
-        compatibility: the full matrix is kept on the device.
+        combined with one all-reduce of the packed triangle.  ``use_specialized_matmul`` rounds the rows to float32 before the product, as
+        upstream's matmul_and_reduce path does (the products are still accumulated in float64).  ``ntiles`` is accepted
+        for signature compatibility: the full matrix is kept on the device.
         """
         from .. import cabi
         from ..utils.sharding import my_shard
@@ -251,7 +252,13 @@ class BaseKernel():
             else:
                 targets = torch.cat((data['energies'], data['forces'].flatten()))
             rows = Ztrain if Gtrain is None else torch.cat((Ztrain, Gtrain.reshape(-1, nf)), dim=0)
-            cabi.normal_equations_accumulate(rows, targets.contiguous(), ZTZ, ZtrainY)
+            if use_specialized_matmul:
+                # upstream hands float32 copies of the rows to matmul_and_reduce (kernel.py:176-188); Z^T y keeps the
+                # float64 rows (kernel.py:192)
+                cabi.normal_equations_accumulate(rows.float().double(), None, ZTZ, None)
+                cabi.gemv_t(rows, targets.contiguous(), ZtrainY)
+            else:
+                cabi.normal_equations_accumulate(rows, targets.contiguous(), ZTZ, ZtrainY)
         if distributed:
             self.allreduce_normal_equations(ZTZ, ZtrainY)       # packed triangle over the ranks, mirrored afterwards
         else:

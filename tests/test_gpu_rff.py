@@ -198,3 +198,70 @@ def test_rff_golden_vectors_on_gpu():
     A = data['charges'].shape[1]
     assert np.abs(Zt.cpu().numpy() - g['c0_Zrows']).max() <= 2e-6
     assert np.abs(Gt.cpu().numpy() - g['c0_Grows'][:, :A]).max() <= 2e-5 * max(1.0, float(np.abs(g['c0_Grows']).max()))
+
+
+def test_rff_training_rows_full_width():
+    """Training rows at the benchmark width (npcas 256, 16,384 features): against the float64 oracle from coordinates on
+    sampled features, and -- fed with the kernel's own float32 inputs -- against a float64 evaluation of upstream's
+    formula (cuda/random_features_kernel.cu:5-94: float64 dot products of float32 inputs), which the kernel must
+    reproduce to float64 rounding.  Prints how far a float32 evaluation of the same rows would be."""
+    import qml_lightning_b200 as q
+    from oracle import training_rows
+    from qml_lightning_b200 import cabi
+    X, Z, c, species = H.batch_c1(4, seed=41)
+    p = H.fchl_params(species)
+    npcas, D = 256, 16384
+    ref = H.rff_model(X, Z, c, p, species, npcas, D)
+    rep = q.FCHLCuda(species=np.array(species), rcut=p.rcut, nRs2=p.nRs2, nRs3=p.nRs3, eta2=p.eta2, eta3=p.eta3,
+                     two_body_decay=p.two_body_decay, three_body_weight=p.three_body_weight,
+                     three_body_decay=p.three_body_decay, device=DEV)
+    m = q.RandomFourrierFeaturesModel(rep=rep, elements=np.array(species), sigma=2.0, nstacks=D // npcas, npcas=npcas)
+    m.reductors, m.W, m.b = ref['reductors'].to(DEV), ref['W'].to(DEV), ref['b'].to(DEV)
+    counts = c.tolist()
+    data = m.format_data([X[i, :counts[i]].numpy() for i in range(len(counts))], [Z[i, :counts[i]].numpy() for i in range(len(counts))])
+    Zt, Gt = m.training_rows(data, with_forces=True)
+    nb, A = data['charges'].shape
+    # (1) from coordinates, sampled features: the oracle normalises by its own feature count
+    idx = torch.tensor([0, 63, 64, 4097, 9999, 16383])
+    sub = dict(ref, W=ref['W'][..., idx].contiguous(), b=ref['b'][..., idx].contiguous(), alpha=ref['alpha'][idx])
+    Zr, Gr = training_rows(X, Z, c, p, sub)
+    scale = math.sqrt(len(idx) / D)
+    Zr, Gr = Zr * scale, Gr * scale
+    assert (Zt.cpu()[:, idx] - Zr).abs().max() <= 2e-6 * max(float(Zr.abs().max()), 1e-2)
+    assert (Gt.cpu()[..., idx] - Gr[:, :A]).abs().max() <= 2e-5 * float(Gr.abs().max())
+    # (2) stage level, identical float32 inputs, all features
+    Xd, Zd, cd = data['coordinates'], data['charges'], data['natom_counts']
+    kp = rep.kernel_params(DEV)
+    g = cabi.group_by_element(Zd, cd, m.species, data['atomIDs'].shape[0])
+    rep_rows, jac_rows = cabi.fchl19_forward_jacobian(Xd, Zd, cd, kp, grouping=g)
+    dx = cabi.pca_project_jacobian(jac_rows, m.reductors, g)
+    x = cabi.pca_project(rep_rows, m.reductors, g)
+    Z2, G2 = cabi.rff_train_features(x, dx, m.W, m.b, g, cd, nb, A)
+    assert torch.equal(Z2, Zt) and torch.equal(G2, Gt)
+    normf = math.sqrt(2.0 / D)
+    Z64 = torch.zeros(nb, D, dtype=torch.float64, device=DEV)
+    G64 = torch.zeros(nb, A, 3, D, dtype=torch.float64, device=DEV)
+    Z32 = torch.zeros(nb, D, dtype=torch.float64, device=DEV)
+    G32 = torch.zeros(nb, A, 3, D, dtype=torch.float64, device=DEV)
+    tf32 = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    sor, gs = g.slot_of_row.cpu(), g.group_start.cpu()
+    for e in range(len(species)):
+        for row in range(int(gs[e]), int(gs[e + 1])):
+            slot = int(sor[row])
+            if slot < 0:
+                continue
+            mol = slot // A
+            arg = x[row].double() @ m.W[e].double() + m.b[e].double()
+            Z64[mol] += normf * torch.cos(arg)
+            G64[mol] += normf * torch.sin(arg) * (dx[row].double() @ m.W[e].double())
+            arg32 = x[row] @ m.W[e] + m.b[e]
+            Z32[mol] += (normf * torch.cos(arg32)).double()
+            G32[mol] += (normf * torch.sin(arg32) * (dx[row] @ m.W[e])).double()
+    torch.backends.cuda.matmul.allow_tf32 = tf32
+    gmax, zmax = float(G64.abs().max()), float(Z64.abs().max())
+    print(f"RFF rows at K=256, D=16384: kernel vs float64 formula: Z {float((Zt - Z64).abs().max()) / zmax:.2e}, "
+          f"G {float((Gt - G64).abs().max()) / gmax:.2e}; a float32 evaluation: Z {float((Z32 - Z64).abs().max()) / zmax:.2e}, "
+          f"G {float((G32 - G64).abs().max()) / gmax:.2e} (relative to the largest entry)")
+    assert (Zt - Z64).abs().max() <= 1e-12 * zmax
+    assert (Gt - G64).abs().max() <= 1e-12 * gmax
