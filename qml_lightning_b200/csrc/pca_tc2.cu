@@ -38,6 +38,12 @@ constexpr int MMA_WARP = 8;      // warp 8: MMA issue (+ tensor-memory allocatio
 constexpr int NTHREADS = 320;
 constexpr int NSTAGES = 2;
 constexpr int WAIT_LIMIT = 1 << 22;
+// Polls granted to the very first wait of the MMA warp.  The product build uses the common limit; the failure-detection
+// test builds this file with zero polls so that this one wait runs out while nothing has been issued yet, which
+// exercises the give-up path (skip the results, drain, free the tensor memory, count) without a fault or a hang.
+#ifndef QMLB_TEST_FIRST_WAIT_POLLS
+#define QMLB_TEST_FIRST_WAIT_POLLS WAIT_LIMIT
+#endif
 constexpr uint32_t TMEM_COLS = 512, COL_MAIN = 0, COL_CROSS = 256;
 constexpr uint32_t A_HALF = BM * BK * 4;           // A hi (or lo) image of one chunk: 16 KB
 static_assert(BM == QMLB_ROW_TILE, "a block must cover exactly one row tile");
@@ -74,8 +80,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 // Bounded parity wait; false on time-out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (int it = 0; it < WAIT_LIMIT; ++it) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int limit = WAIT_LIMIT) {
+    for (int it = 0; it < limit; ++it) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -163,6 +169,19 @@ __global__ void pca_pack_kernel(const float *__restrict__ P, int nel, int repsiz
 // ---------------------------------------------------------------------------------------------------------------
 // main kernel
 // ---------------------------------------------------------------------------------------------------------------
+// A block that gives up (or belongs to a launch in which another block did) must not leave its output tile as it found
+// it: the caller reads energies and gradients without asking qmlb_tc_timeouts(), so the tile is filled with NaN, which
+// travels through every later stage into the energies and gradients of the molecules concerned.
+__device__ __forceinline__ void poison_tile(float *out, int row0, int tile, const Tiling &t, int tid) {
+    if (tid >= 2 * BM) return;
+    const int r = tid % BM, h = tid / BM, half = t.NT / 2;
+    const float nan = __int_as_float(0x7fc00000);
+    for (int c = 0; c < half; ++c) {
+        const int col = tile * t.NT + h * half + c;
+        if (col < t.Nout) out[(size_t)(row0 + r) * t.Nout + col] = nan;
+    }
+}
+
 enum { A_FULL = 0, B_FULL = A_FULL + NSTAGES, STAGE_FREE = B_FULL + NSTAGES, ACC_FULL = STAGE_FREE + NSTAGES, ACC_FREE, ALL_DONE, NBARS };
 
 // 10 warps = 3 per SM sub-partition at most, whose 16,384 registers allow 168 per thread; the register row of the drain
@@ -178,7 +197,10 @@ pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ p
     const int row0 = blockIdx.x * BM;
     const int tile = blockIdx.y;
     if (row0 >= group_start[nel]) return;
-    if (*reinterpret_cast<volatile unsigned *>(&g_pca_tc2_failed_launch) == launch_seq) return;
+    if (*reinterpret_cast<volatile unsigned *>(&g_pca_tc2_failed_launch) == launch_seq) {
+        poison_tile(out, row0, tile, t, threadIdx.x);
+        return;
+    }
     int e = 0;
     while (e + 1 < nel && row0 >= group_start[e + 1]) ++e;
     const unsigned char *blobs = packed + ((size_t)e * t.ntiles + tile) * t.nchunks * t.chunk_bytes;
@@ -315,8 +337,8 @@ pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ p
             const uint32_t par = (uint32_t)(c / NSTAGES) & 1u;
             const int g = c / group_chunks;
             const bool first = (c % group_chunks) == 0;
-            bool w = mbar_wait(bar(A_FULL + s), par);
-            w = mbar_wait(bar(B_FULL + s), par) && w;
+            bool w = mbar_wait(bar(A_FULL + s), par, c == 0 ? QMLB_TEST_FIRST_WAIT_POLLS : WAIT_LIMIT);
+            w = w && mbar_wait(bar(B_FULL + s), par);
             if (first && g > 0) w = mbar_wait(bar(ACC_FREE), (uint32_t)(g - 1) & 1u) && w;
             if (!__all_sync(QMLB_FULL_MASK, w)) { ok = false; break; }
             fence_after();
@@ -365,9 +387,12 @@ pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ p
     fence_before();
     __syncthreads();
     fence_after();
-    if (failed && tid == 0) {
-        atomicAdd(&g_pca_tc2_timeouts, 1);
-        atomicExch(&g_pca_tc2_failed_launch, launch_seq);
+    if (failed) {
+        poison_tile(out, row0, tile, t, tid);
+        if (tid == 0) {
+            atomicAdd(&g_pca_tc2_timeouts, 1);
+            atomicExch(&g_pca_tc2_failed_launch, launch_seq);
+        }
     }
     if (warp == MMA_WARP) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_alloc), "r"(TMEM_COLS) : "memory");

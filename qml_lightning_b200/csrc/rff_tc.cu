@@ -301,13 +301,27 @@ rff_tc_kernel(const float *__restrict__ x, const int *__restrict__ group_start, 
 
     const int row0 = blockIdx.x * BM;
     if (row0 >= group_start[nel]) return;
-    if (*reinterpret_cast<volatile unsigned *>(&g_rff_tc_failed_launch) == launch_seq) return;
+    // A block that cannot deliver its rows fills them with NaN: the caller reads energies and gradients without asking
+    // qmlb_tc_timeouts(), and NaN travels through the remaining stages into the molecules concerned.
+    auto poison = [&]() {
+        const float nan = __int_as_float(0x7fc00000);
+        for (int i = threadIdx.x; i < BM * (K + 1); i += NTHREADS) {
+            const int r = i / (K + 1), c = i % (K + 1);
+            if (c == K) atom_energy[row0 + r] = nan;
+            else grad_x[(size_t)(row0 + r) * K + c] = nan;
+        }
+    };
+    if (*reinterpret_cast<volatile unsigned *>(&g_rff_tc_failed_launch) == launch_seq) {
+        poison();
+        return;
+    }
     int e = 0;
     while (e + 1 < nel && row0 >= group_start[e + 1]) ++e;
 
     const PackHeader *hdr = reinterpret_cast<const PackHeader *>(packed);
     if (hdr->npcas != K || hdr->nelements != nel) {  // parameters packed for another model: refuse, and say so
         if (threadIdx.x == 0) atomicAdd(&g_rff_tc_timeouts, 1);
+        poison();
         return;
     }
     const int nchunks = hdr->nchunks;
@@ -604,9 +618,12 @@ rff_tc_kernel(const float *__restrict__ x, const int *__restrict__ group_start, 
     fence_before();
     __syncthreads();
     fence_after();
-    if (failed && tid == 0) {
-        atomicAdd(&g_rff_tc_timeouts, 1);
-        atomicExch(&g_rff_tc_failed_launch, launch_seq);
+    if (failed) {
+        poison();
+        if (tid == 0) {
+            atomicAdd(&g_rff_tc_timeouts, 1);
+            atomicExch(&g_rff_tc_failed_launch, launch_seq);
+        }
     }
     if (warp == MMA_WARP) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_alloc), "r"(TMEM_COLS) : "memory");

@@ -123,35 +123,58 @@ class BaseKernel():
         self.self_energy[species] = beta
 
     # ---- projection matrices ---------------------------------------------------------------------------------
+    def sample_representations(self, X, Q, element, pick, cells=None, inv_cells=None, npca_choice=256, nsamples=4096):
+        """Rows ``f32[n, repsize]`` of the SVD sample matrix of ``element`` for the molecules ``pick`` (see
+        ``get_reductors`` for the rule); everything up to the final row gather runs on the device without a host wait."""
+        from .. import cabi
+        dev = self.rep.device
+        data = self.format_data([X[i] for i in pick], [Q[i] for i in pick],
+                                cells=None if cells is None else [cells[i] for i in pick],
+                                inv_cells=None if inv_cells is None else [inv_cells[i] for i in pick])
+        Zc, counts = data['charges'], data['natom_counts']
+        A = Zc.shape[1]
+        one = torch.tensor([float(element)], dtype=torch.float32, device=dev)
+        g = cabi.group_by_element(Zc, counts, one, data['atomIDs'].shape[0])          # rows = the atoms of this element
+        rows = torch.zeros(g.rows_cap, self.rep.get_repsize(), dtype=torch.float32, device=dev)
+        cabi.fchl19_forward(data['coordinates'], Zc, counts, self.rep.kernel_params(dev), data['cells'], data['inv_cells'],
+                            row_of_slot=g.row_of_slot, out=rows)
+        slot = g.slot_of_row.long()
+        real = slot >= 0
+        nbatches = (len(pick) + self.nbatch_train - 1) // self.nbatch_train
+        batch = torch.where(real, torch.div(slot, A, rounding_mode='floor') // self.nbatch_train,
+                            torch.full_like(slot, nbatches))                           # padding rows sort last
+        # random order inside every batch: sort by (batch, random key); rank = position within the batch
+        key = batch.double() + torch.rand(slot.shape[0], device=dev, dtype=torch.float64) * 0.5
+        order = torch.argsort(key)
+        sorted_batch = batch[order]
+        per_batch = torch.bincount(sorted_batch, minlength=nbatches + 1)[:nbatches]
+        first = torch.cumsum(per_batch, 0) - per_batch
+        rank = torch.arange(slot.shape[0], device=dev) - first[sorted_batch.clamp(max=nbatches - 1)]
+        taken = torch.clamp(per_batch, max=npca_choice)
+        before = torch.cumsum(taken, 0) - taken                                        # atoms collected before each batch
+        batch_ok = before <= nsamples                                                  # upstream stops once nselected > nsamples
+        keep = (sorted_batch < nbatches) & (rank < npca_choice) & batch_ok[sorted_batch.clamp(max=nbatches - 1)]
+        return rows[order[keep]]                                                       # the one host wait: its row count
+
     def get_reductors(self, X, Q, cells=None, inv_cells=None, npcas=128, npca_choice=256, nsamples=4096, print_info=True):
-        """Per element: SVD of sampled atom representations, first ``npcas`` left singular vectors
-        (sampling rule of upstream kernel.py:447-540: up to 1024 molecules containing the element, at most
-        ``npca_choice`` atoms per batch, stop after ``nsamples``)."""
+        """Per element: SVD of sampled atom representations, first ``npcas`` left singular vectors.
+
+        Sampling rule of upstream kernel.py:447-540: up to 1024 molecules containing the element (drawn with
+        replacement by numpy, like upstream), cut into batches of ``nbatch_train`` molecules; from every batch at most
+        ``npca_choice`` randomly chosen atoms of the element; batches are taken until more than ``nsamples`` atoms have
+        been collected.  Upstream formats every batch, evaluates the representation per batch and gathers the rows with
+        boolean masks (one host synchronisation per batch); here the picked molecules are formatted once, the
+        representation is written straight into element-grouped rows by one kernel launch, and the per-batch selection
+        is index arithmetic on the device, so the host waits once per element (for the size of the sample matrix)."""
         for e in self.elements:
             ei = int(self.element2index[int(e)])
             have = np.array([i for i in range(len(Q)) if int(e) in np.asarray(Q[i])], dtype=np.int64)
             if have.size == 0:
                 continue
             pick = np.random.choice(have, size=min(len(have), 1024))
-            inputs, nselected = [], 0
-            for s in range(0, len(pick), self.nbatch_train):
-                if nselected > nsamples:
-                    break
-                idx = pick[s:s + self.nbatch_train]
-                data = self.format_data([X[i] for i in idx], [Q[i] for i in idx],
-                                        cells=None if cells is None else [cells[i] for i in idx],
-                                        inv_cells=None if inv_cells is None else [inv_cells[i] for i in idx])
-                rep = self.rep.get_representation(data['coordinates'], data['charges'], data['atomIDs'], data['molIDs'],
-                                                  data['natom_counts'], data['cells'], data['inv_cells'])
-                rows = rep[data['charges'] == float(e)]
-                if rows.shape[0] == 0:
-                    continue
-                rows = rows[torch.randperm(rows.size(0), device=rows.device)[:npca_choice]]
-                nselected += rows.shape[0]
-                inputs.append(rows)
-            if not inputs:
+            mat = self.sample_representations(X, Q, int(e), pick, cells, inv_cells, npca_choice, nsamples)
+            if mat.shape[0] == 0:
                 continue
-            mat = torch.cat(inputs)
             u, s, _ = torch.linalg.svd(mat.T, full_matrices=False)
             if print_info:
                 cev = 100 - (s.sum() - s[:npcas].sum()) / s.sum() * 100

@@ -277,3 +277,49 @@ def test_upstream_archive_loads_and_predicts():
 def test_upstream_archive_force_criterion_component_wise():
     u, total, F = _run_archive()
     assert np.isclose(u['ref_forces'], F, rtol=1e-4, atol=1e-4).all(), _report('archive vs fixture', F, u['ref_forces'])
+
+
+def test_get_reductors_sampling_rule_and_subspace():
+    """Device-side construction of the projection matrices (upstream models/kernel.py:447-540): the per-batch cap, the
+    stop rule, membership of the sampled rows, and -- when every atom is taken -- the same subspace as an SVD of all
+    rows of the element."""
+    import qml_lightning_b200 as q
+    from qml_lightning_b200 import cabi
+    X, Z, c, species = H.batch_mixed(60, seed=33, max_atoms=12)
+    rep = q.FCHLCuda(species=np.array(species), nRs2=8, nRs3=6, device=DEV)
+    model_elements = [1, 6, 8]                                  # the rarer species have too few atoms here for 16 vectors
+    m = q.HadamardFeaturesModel(rep=rep, elements=np.array(model_elements), ntransforms=1, sigma=2.0, npcas=16, nstacks=2,
+                                nbatch_train=8)
+    Xl = [X[i, :int(c[i])].numpy() for i in range(60)]
+    Zl = [Z[i, :int(c[i])].numpy() for i in range(60)]
+    e = 6
+    pick = np.array([i for i in range(60) if e in Zl[i]])
+    full = cabi.fchl19_forward(X.to(DEV), Z.to(DEV), c.to(DEV), rep.kernel_params(DEV))
+    per_batch = [int(sum((Zl[i] == e).sum() for i in pick[b:b + 8])) for b in range(0, len(pick), 8)]
+    # cap of 3 atoms per batch, stop once more than 10 atoms are collected
+    mat = m.sample_representations(Xl, Zl, e, pick, npca_choice=3, nsamples=10)
+    want, total = 0, 0
+    for n in per_batch:
+        if total > 10:
+            break
+        want += min(n, 3)
+        total += min(n, 3)
+    assert mat.shape[0] == want
+    allrows = full[torch.from_numpy(pick).to(DEV)][(Z[pick] == e).to(DEV)]
+    d = torch.cdist(mat.double(), allrows.double()).min(dim=1).values
+    assert float(d.max()) <= 1e-6 * float(allrows.abs().max())         # every sampled row is a row of the element
+    # everything taken: same subspace as the SVD of all rows (duplicates do not change the left singular vectors' span)
+    np.random.seed(3)
+    m.get_reductors(Xl, Zl, npcas=16, npca_choice=4096, nsamples=10 ** 6, print_info=False)
+    np.random.seed(3)
+    for el in model_elements:
+        have = np.array([i for i in range(60) if el in Zl[i]])
+        pk = np.random.choice(have, size=min(len(have), 1024))
+        rows = torch.cat([full[i][(Z[i] == el).to(DEV)] for i in pk]).double()
+        u, s, _ = torch.linalg.svd(rows.T, full_matrices=False)
+        U = m.reductors[int(m.element2index[el])].double()
+        ortho = float((U.T @ U - torch.eye(16, device=DEV, dtype=torch.float64)).abs().max())
+        assert ortho <= 1e-3, (el, ortho)                                # float32 Jacobi SVD of the library (as upstream)
+        if float(s[15] - s[16]) > 1e-3 * float(s[0]):                   # subspace well defined
+            P1, P2 = U @ U.T, u[:, :16] @ u[:, :16].T
+            assert float((P1 - P2).abs().max()) <= 5e-3
