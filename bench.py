@@ -69,6 +69,8 @@ def parse_args():
     ap.add_argument('--cpu-sample', type=int, default=256, help='conformers of the CPU-baseline sample')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-extras', action='store_true', help='headline workload only')
+    ap.add_argument('--nstacks', type=int, default=0, help='c4 only: override the stack count (small cases for profiling)')
+    ap.add_argument('--rows-only', action='store_true', help='c4 only: training rows without the normal equations')
     return ap.parse_args()
 
 
@@ -421,13 +423,14 @@ def rff_roofline(r):
                                / (r['ms'] * 1e-3) / 1e12}
 
 
-def run_c4(dev, dist, rank, world, nconf):
+def run_c4(dev, dist, rank, world, nconf, nstacks_override=0, rows_only=False):
     """Training normal equations at 32,768 features: ``nconf`` conformers on every rank (64 rows each), accumulated with
     the in-tree float64 kernel (and, for comparison, cuBLAS DSYRK on the same rows), one all-reduce of the packed
     triangle, the Cholesky solve on rank 0 and the broadcast of the weights."""
     from qml_lightning_b200 import cabi
     from qml_lightning_b200.utils import distributed as D
     species, npcas, nstacks, _, _ = WORKLOADS['c4']
+    nstacks = nstacks_override or nstacks
     X, Z, counts = workload(nconf, 1004 + rank, 'c1')
     rep, model = build_model(dev, X, Z, counts, species, npcas, nstacks)
     F = npcas * nstacks
@@ -447,6 +450,9 @@ def run_c4(dev, dist, rank, world, nconf):
 
     model.training_rows(data, with_forces=True)                                  # warm-up
     (Ztrain, Gtrain), rows_ms = timed(lambda: model.training_rows(data, with_forces=True))
+    if rows_only:
+        return {'workload': 'c4', 'features': F, 'conformers_per_gpu': nconf, 'training_rows_ms': dist.max([rows_ms])[0],
+                'conformers_per_s': nconf * world / (rows_ms * 1e-3), 'accumulate_ms': 0.0}
     rows = torch.cat((Ztrain, Gtrain.reshape(-1, F)), dim=0)
     targets = torch.cat((data['energies'], data['forces'].flatten())).contiguous()
     del Ztrain, Gtrain
@@ -526,7 +532,7 @@ def main():
     species, npcas, nstacks, default_n, _ = WORKLOADS[name]
     nreq = args.conformers or default_n
     if name == 'c4':
-        out = run_c4(dev, dist, rank, world, nreq)
+        out = run_c4(dev, dist, rank, world, nreq, args.nstacks, args.rows_only)
         if rank == 0:
             print(json.dumps({'metric': 'normal-equation accumulation', 'value': out['conformers_per_s'], 'unit': 'conformers/s',
                               'n_gpus': world, 'steps': 1, 'warmup': 1, 'ms_per_step': out['training_rows_ms'] + out['accumulate_ms'],
