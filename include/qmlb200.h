@@ -161,7 +161,9 @@ int qmlb_group_by_element_noalloc(const float *Z, const int *atom_counts, const 
 int qmlb_pca_project(const float *in, const float *reductors, const int *group_start, int nelements, size_t rows_cap,
                      int repsize, int npcas, int transpose, float *out, qmlb_stream_t stream);
 
-/* The same contraction on the 5th-generation tensor cores: tcgen05.mma kind::tf32 with the accumulator in tensor
+/* SUPERSEDED by qmlb_pca_pack / qmlb_pca_project_packed below (same arithmetic, pre-split projection matrices, wider
+ * tiles); kept as an independent tensor-core implementation that the tests cross-check the newer one against.
+ * The same contraction on the 5th-generation tensor cores: tcgen05.mma kind::tf32 with the accumulator in tensor
  * memory and a 3xTF32 operand split (fp32-accurate result).  sub_rows = matrix rows per grouped row (1 for
  * representations and gradients, 3*A for Jacobians).  qmlb_tc_timeouts() returns how many blocks ever gave up on a
  * bounded wait (0 in a healthy run; it synchronises the device). */
@@ -262,7 +264,8 @@ int qmlb_rff_energy_grad(const float *x, const int *group_start, const int *slot
  * qmlb_rff_pack must be called again whenever W, b or alpha change.  Feature counts are padded to a multiple of 32
  * inside the packed buffer (padding features carry zero weight).  qmlb_rff_pack_bytes returns 0 for unsupported
  * sizes.  Operands larger than 2^41 in magnitude are outside the supported range.  A kernel that is handed parameters
- * packed for another npcas or element count does nothing and reports through qmlb_tc_timeouts(). */
+ * packed for another npcas or element count, or a block that gives up on one of its bounded waits, fills its rows of
+ * atom_energy and grad_x with NaN and reports through qmlb_tc_timeouts(). */
 size_t qmlb_rff_pack_bytes(int nelements, int npcas, int nfeatures);
 int qmlb_rff_pack(const float *W, const float *b, const float *alpha, int nelements, int npcas, int nfeatures, void *packed,
                   size_t packed_bytes, qmlb_stream_t stream);

@@ -154,3 +154,62 @@ def test_normal_equations_full_width_linearity():
     assert float((A1 - A2).abs().max()) <= 1e-10 * scale
     assert float((A1 - A1.T).abs().max()) == 0.0
     assert float((y1 - y2).abs().max()) <= 1e-10 * float(y1.abs().max())
+
+
+def test_normal_equations_full_width_against_float64_matmul():
+    """One c4 row block (64 conformers x 64 rows = 4,096 rows, 32,768 features) through the in-tree float64 kernel
+    against ``torch.matmul`` in float64 on the same rows: 1e-10 relative on the upper triangle (the benchmark
+    contract), the lower triangle untouched, Z^T y likewise; the specialised path differs by float32 rounding only."""
+    from qml_lightning_b200 import cabi
+    gen = torch.Generator(device=DEV).manual_seed(4)
+    rows, F = 4096, 32768
+    M = torch.randn(rows, F, generator=gen, device=DEV, dtype=torch.float64) * torch.logspace(-2, 0, F, device=DEV, dtype=torch.float64)
+    y = torch.randn(rows, generator=gen, device=DEV, dtype=torch.float64)
+    ZTZ = torch.zeros(F, F, device=DEV, dtype=torch.float64)
+    ZTy = torch.zeros(F, 1, device=DEV, dtype=torch.float64)
+    cabi.normal_equations_accumulate(M, y, ZTZ, ZTy)
+    refy = M.T @ y[:, None]
+    assert float((ZTy - refy).abs().max()) <= 1e-10 * float(refy.abs().max())
+    scale = None
+    for c0 in range(0, F, 4096):                                   # column panels: the reference never needs a second 8.6 GB matrix
+        ref = M.T @ M[:, c0:c0 + 4096]                             # [F, 4096]
+        got = ZTZ[:, c0:c0 + 4096]
+        scale = float(ref.abs().max()) if scale is None else max(scale, float(ref.abs().max()))
+        i = torch.arange(F, device=DEV)[:, None]
+        j = c0 + torch.arange(4096, device=DEV)[None, :]
+        upper = j >= i
+        assert float(((got - ref) * upper).abs().max()) <= 1e-10 * scale
+        assert float((got * (~upper)).abs().max()) == 0.0
+        del ref, got, upper
+    cabi.symmetrize_upper(ZTZ)
+    assert float((ZTZ[:4096, :4096] - ZTZ[:4096, :4096].T).abs().max()) == 0.0
+
+
+def test_sorf_training_rows_full_width():
+    """SORF training rows at the training configuration's width (npcas 256, 128 stacks = 32,768 features) against the
+    float64 oracle on two sampled stacks (512 features; the oracle differentiates feature by feature)."""
+    import math
+    import qml_lightning_b200 as q
+    from oracle import training_rows
+    X, Z, c, species = H.batch_c1(3, seed=51)
+    p = H.fchl_params(species)
+    npcas, nstacks = 256, 128
+    ref = H.sorf_model(X, Z, c, p, species, npcas, nstacks)
+    rep = q.FCHLCuda(species=np.array(species), rcut=p.rcut, nRs2=p.nRs2, nRs3=p.nRs3, eta2=p.eta2, eta3=p.eta3,
+                     two_body_decay=p.two_body_decay, three_body_weight=p.three_body_weight,
+                     three_body_decay=p.three_body_decay, device=DEV)
+    m = q.HadamardFeaturesModel(rep=rep, elements=np.array(species), ntransforms=1, sigma=ref['sigma'], npcas=npcas, nstacks=nstacks)
+    m.reductors, m.Dmat, m.bias = ref['reductors'].to(DEV), ref['Dmat'].to(DEV), ref['bias'].to(DEV)
+    m.set_alpha(ref['alpha'].to(DEV))
+    counts = c.tolist()
+    data = m.format_data([X[i, :counts[i]].numpy() for i in range(len(counts))], [Z[i, :counts[i]].numpy() for i in range(len(counts))])
+    Zt, Gt = m.training_rows(data, with_forces=True)
+    A = data['charges'].shape[1]
+    stacks = [5, 127]
+    cols = torch.cat([torch.arange(s * npcas, (s + 1) * npcas) for s in stacks])
+    sub = dict(ref, Dmat=ref['Dmat'][:, :, stacks].contiguous(), bias=ref['bias'][:, cols].contiguous(), alpha=ref['alpha'][cols])
+    Zr, Gr = training_rows(X, Z, c, p, sub)
+    scale = math.sqrt(len(cols) / (npcas * nstacks))               # the oracle normalises by its own feature count
+    Zr, Gr = Zr * scale, Gr * scale
+    assert (Zt.cpu()[:, cols] - Zr).abs().max() <= 2e-6 * max(float(Zr.abs().max()), 1e-2)
+    assert (Gt.cpu()[..., cols] - Gr[:, :A]).abs().max() <= 2e-5 * float(Gr.abs().max())
