@@ -19,7 +19,10 @@ configurations, each measured in the same process after the headline:
 * ``c4``  training: float64 normal equations at 32,768 features -- accumulation of 64 conformers per rank (in-tree
           DMMA kernel and cuBLAS DSYRK back to back), the NCCL all-reduce of the packed triangle, the solve on rank 0;
 * at N = 1 also ``c0`` (1,000 9-atom conformers), ``c3`` (RFF model, 100,000 conformers, tensor-core kernel against
-  the measured dense bf16 rate) and ``c1_accurate`` (the headline with accurate sin/cos instead of the SFU).
+  the measured dense bf16 rate), ``c1_accurate`` (the headline with accurate sin/cos instead of the SFU) and
+  ``reference_cuda``: upstream's own CUDA operators with the 72-byte shared-memory allocation fix of
+  baseline/build_ref.py, timed on identical inputs in a child process, with the three parity distances (present only
+  when those operator libraries have been built).
 
 ``--impl reference`` times the CPU oracle alone, without touching CUDA (the upstream project has no CPU implementation
 of this path, so the oracle port is the CPU reference).
@@ -503,6 +506,26 @@ def run_c4(dev, dist, rank, world, nconf, nstacks_override=0, rows_only=False):
             'solver': 'Cholesky (potrf + potrs, fp64) on rank 0, weights broadcast; llambda 1e-5'}
 
 
+def reference_cuda_comparison():
+    """Upstream's own CUDA operators ("reference + 72-byte allocation fix", built by baseline/build_ref.py into the
+    git-ignored baseline/_ref/) against this library on identical inputs, each workload in a child process
+    (baseline/compare_ref_cuda.py).  Reported when the two operator libraries are present; a failure of the child is
+    recorded, never fatal."""
+    libs = [os.path.join(ROOT, 'baseline', '_ref', n) for n in ('libref_torchscript_fchl19.so', 'libref_torchscript_sorf.so')]
+    if not all(os.path.exists(p) for p in libs):
+        return {'unavailable': 'baseline/_ref operator libraries not built (python baseline/build_ref.py needs an upstream checkout)'}
+    out = {'label': 'reference + 72-byte allocation fix (upstream sources otherwise unchanged, -O2, sm_100a)'}
+    for name, nmol, batch in (('c0', 1000, 1000), ('c1', 2000, 1000)):
+        try:
+            r = subprocess.run([sys.executable, os.path.join(ROOT, 'baseline', 'compare_ref_cuda.py'), '--workload', name, '--nmol', str(nmol),
+                                '--batch', str(batch)], capture_output=True, text=True, timeout=600)
+            lines = [ln for ln in r.stdout.splitlines() if ln.startswith('{')]
+            out[name] = json.loads(lines[-1]) if lines else {'unavailable': (r.stderr or r.stdout)[-300:]}
+        except Exception as exc:  # noqa: BLE001  (a comparison that cannot run must not take the benchmark down)
+            out[name] = {'unavailable': repr(exc)[:300]}
+    return out
+
+
 def extra_entry(r, world, sm_mhz, scaling):
     out = {'value': r['value'], 'unit': 'molecules/s', 'ms_per_step': r['ms'], 'scaling': scaling,
            'e2e': None if r['e2e_value'] is None else {'value': r['e2e_value'], 'unit': 'molecules/s',
@@ -604,6 +627,9 @@ def main():
             del e
             torch.cuda.empty_cache()
         extra['c4'] = run_c4(dev, dist, rank, world, WORKLOADS['c4'][3])
+        if world == 1:
+            torch.cuda.empty_cache()
+            extra['reference_cuda'] = reference_cuda_comparison()
         line['extra'] = extra
     if rank == 0:
         print(json.dumps(line))
