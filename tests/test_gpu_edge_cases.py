@@ -116,3 +116,26 @@ def test_large_molecule_and_shared_memory_limit():
     with pytest.raises(RuntimeError, match='shared memory'):
         cabi.fchl19_forward(torch.zeros(1, big, 3, device=DEV), torch.zeros(1, big, device=DEV),
                             torch.zeros(1, dtype=torch.int32, device=DEV), kp)
+
+
+def test_row_capacity_too_small_gives_nan_not_wrong_numbers():
+    """``atomIDs`` shorter than the batch (the row capacity is derived from its length): the molecules whose atoms found
+    no row come back as NaN in energies and gradients, every other molecule is unchanged, nothing is dropped silently."""
+    from qml_lightning_b200 import cabi
+    X, Z, c, species = H.batch_c0(200, seed=61)
+    p = H.fchl_params(species)
+    kp = H.kernel_params(p, DEV)
+    model = H.sorf_model(X, Z, c, p, species, 64, 4)
+    packed = cabi.sorf_pack(model['Dmat'].to(DEV), model['bias'].to(DEV), model['alpha'].to(DEV))
+    el = torch.tensor(species, dtype=torch.float32, device=DEV)
+    args = (X.to(DEV), Z.to(DEV), c.to(DEV), kp, el, model['reductors'].to(DEV), packed, 4, 1, model['sigma'])
+    E_full, G_full = cabi.sorf_predict(*args)
+    total = int(c.sum())
+    # 200 molecules x 9 atoms = 1,800 atoms in 1280 (H) + 512 (C) + 256 (O) = 2,048 element-grouped rows; claiming 1,500
+    # atoms gives 1,920 rows: the oxygen atoms of the last molecules find no row
+    E, G = cabi.sorf_predict(*args, n_atoms_upper=1500)
+    torch.cuda.synchronize()
+    bad = torch.isnan(E)
+    assert bool(bad.any()) and not bool(bad.all()), (int(bad.sum()), total)
+    assert torch.equal(torch.isnan(G).flatten(1).any(dim=1), bad)               # the same molecules in the gradient
+    assert torch.allclose(E[~bad], E_full[~bad], rtol=0, atol=0) and torch.equal(G[~bad], G_full[~bad])
