@@ -69,7 +69,7 @@ def parse_args():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--workload', default='c1', choices=sorted(WORKLOADS))
     ap.add_argument('--conformers', type=int, default=0, help='molecules per GPU (0 = the workload default)')
-    ap.add_argument('--cpu-sample', type=int, default=256, help='conformers of the CPU-baseline sample')
+    ap.add_argument('--cpu-sample', type=int, default=1000, help='conformers of the CPU-baseline sample')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-extras', action='store_true', help='headline workload only')
     ap.add_argument('--nstacks', type=int, default=0, help='c4 only: override the stack count (small cases for profiling)')
