@@ -195,9 +195,13 @@ class BaseKernel():
         red = self.reductors
         key = (red.data_ptr(), red._version, tuple(red.shape), red.device)
         if getattr(self, '_pca_packed_key', None) != key:
-            self._pca_packed = cabi.pca_pair_pack(red.contiguous().float())
+            self._pca_packed = cabi.pca_pair_pack(self.kernel_reductors().contiguous().float())
             self._pca_packed_key = key
         return self._pca_packed
+
+    def kernel_reductors(self):
+        """The projection matrices as the kernels read them; models whose kernels need another width override this."""
+        return self.reductors
 
     # ---- training --------------------------------------------------------------------------------------------
     def training_rows(self, data, with_forces):

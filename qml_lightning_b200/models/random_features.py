@@ -6,13 +6,24 @@ from .. import cabi
 from .kernel import BaseKernel
 
 
+KERNEL_WIDTHS = (32, 64, 128, 256)   # projected widths the feature kernels are built for
+
+
 class RandomFourrierFeaturesModel(BaseKernel, torch.nn.Module):
+    """Any ``npcas`` up to 256 is accepted, as upstream accepts any: the feature kernels exist for 32, 64, 128 and 256
+    projected components, and a model of another width runs on the next of these with zero columns appended to the
+    projection matrices and zero rows to ``W`` (the argument ``x W + b`` is unchanged term by term).  ``reductors``,
+    ``W``, ``b`` and ``alpha`` keep upstream's shapes."""
 
     def __init__(self, rep=None, elements=np.array([1, 6, 7, 8]), sigma=2.0, llambda=1e-10, nstacks=8192, npcas=128,
                  nbatch_train=64, nbatch_test=64, fast_math=True):
         super(RandomFourrierFeaturesModel, self).__init__(rep, npcas, elements, sigma, llambda)
         self.device = rep.device
         self.npcas = npcas
+        widths = [k for k in KERNEL_WIDTHS if k >= npcas]
+        if not widths:
+            raise ValueError(f"npcas must be at most {KERNEL_WIDTHS[-1]}, got {npcas}")
+        self._pad = int(widths[0] - npcas)
         self.nbatch_train = nbatch_train
         self.nbatch_test = nbatch_test
         self._nfeatures = nstacks * self.npcas
@@ -50,26 +61,51 @@ class RandomFourrierFeaturesModel(BaseKernel, torch.nn.Module):
         X, Zc, counts = data['coordinates'], data['charges'], data['natom_counts']
         nb, A = Zc.shape
         kp = self.rep.kernel_params(X.device)
+        red = self.kernel_reductors()
         g = cabi.group_by_element(Zc, counts, self.species, data['atomIDs'].shape[0])
         if with_forces:
             rep_rows, jac_rows = cabi.fchl19_forward_jacobian(X, Zc, counts, kp, data['cells'], data['inv_cells'], grouping=g)
-            dx = cabi.pca_project_jacobian(jac_rows, self.reductors, g)
+            dx = cabi.pca_project_jacobian(jac_rows, red, g)
             del jac_rows
         else:
             rep_rows = torch.zeros(g.rows_cap, self.rep.get_repsize(), dtype=torch.float32, device=X.device)
             cabi.fchl19_forward(X, Zc, counts, kp, data['cells'], data['inv_cells'], row_of_slot=g.row_of_slot, out=rep_rows)
             dx = None
-        x = cabi.pca_project(rep_rows, self.reductors, g)
-        return cabi.rff_train_features(x, dx, self.W, self.b, g, counts, nb, A)
+        x = cabi.pca_project(rep_rows, red, g)
+        return cabi.rff_train_features(x, dx, self._kernel_W(), self.b, g, counts, nb, A)
 
     def _element_features(self, x, dx, element_idx, grouping, counts, nb, A):
         e = element_idx
-        return cabi.rff_train_features(x, dx, self.W[e:e + 1].contiguous(), self.b[e:e + 1].contiguous(), grouping, counts, nb, A)
+        if self._pad > 0:      # rows arrive at the model's own width
+            x = torch.nn.functional.pad(x, [0, self._pad])
+            dx = None if dx is None else torch.nn.functional.pad(dx, [0, self._pad])
+        return cabi.rff_train_features(x, dx, self._kernel_W()[e:e + 1].contiguous(), self.b[e:e + 1].contiguous(), grouping,
+                                       counts, nb, A)
+
+    def kernel_reductors(self):
+        """Projection matrices at the width of the kernels (zero columns appended), cached like :meth:`pca_packed`."""
+        red = self.reductors
+        if self._pad == 0:
+            return red
+        key = (red.data_ptr(), red._version, tuple(red.shape), red.device)
+        if getattr(self, '_red_k_key', None) != key:
+            self._red_k = torch.nn.functional.pad(red.float(), [0, self._pad]).contiguous()
+            self._red_k_key = key
+        return self._red_k
+
+    def _kernel_W(self):
+        if self._pad == 0:
+            return self.W
+        key = (self.W.data_ptr(), self.W._version, tuple(self.W.shape), self.W.device)
+        if getattr(self, '_W_k_key', None) != key:
+            self._W_k = torch.nn.functional.pad(self.W, [0, 0, 0, self._pad]).contiguous()
+            self._W_k_key = key
+        return self._W_k
 
     def _parameters_changed(self):
         """Rebuild the packed image of (W, b, alpha) that the tensor-core feature kernel reads; call after changing any
         of them by hand."""
-        self.packed = torch.ops.qml_lightning_b200.rff_pack(self.W, self.b, self.alpha.float())
+        self.packed = torch.ops.qml_lightning_b200.rff_pack(self._kernel_W(), self.b, self.alpha.float())
 
     # ---- inference -----------------------------------------------------------------------------------------------
     def forward(self, X, Z, atomIDs, molIDs, atom_counts, cell=torch.empty(0, 3, 3), inv_cell=torch.empty(0, 3, 3)):
@@ -77,8 +113,11 @@ class RandomFourrierFeaturesModel(BaseKernel, torch.nn.Module):
         assert X.is_cuda, "X tensor must reside on GPU"
         assert Z.device == X.device, "Z tensor must reside on the same GPU as X"
         assert atom_counts.device == X.device, "atom_counts tensor must reside on the same GPU as X"
+        red = self.reductors
+        if self._pad > 0:
+            red = torch.nn.functional.pad(red, [0, self._pad])
         return torch.ops.qml_lightning_b200.rff_energy(X, Z, atom_counts, cell, inv_cell, self.rep.species, self.rep.Rs2,
-                                                       self.rep.Rs3, self.rep.kernel_scalars, self.species, self.reductors,
+                                                       self.rep.Rs3, self.rep.kernel_scalars, self.species, red,
                                                        self.packed, atomIDs.shape[0], self.fast_math)
 
     def predict_opt(self, coordinates, charges, atomIDs, molIDs, natom_counts, zcells=None, zinv_cells=None, forces=True,
@@ -87,7 +126,7 @@ class RandomFourrierFeaturesModel(BaseKernel, torch.nn.Module):
             raise RuntimeError("must train the model first by calling train()!")
         dev = coordinates.device
         energies, grad = cabi.rff_predict_packed(coordinates, charges, natom_counts, self.rep.kernel_params(dev), self.species,
-                                                 self.reductors, self.packed, zcells, zinv_cells,
+                                                 self.kernel_reductors(), self.packed, zcells, zinv_cells,
                                                  n_atoms_upper=atomIDs.shape[0], fast_math=self.fast_math,
                                                  pca_packed=self.pca_packed())
         if print_info:

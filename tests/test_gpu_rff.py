@@ -84,6 +84,47 @@ def test_rff_predict_and_model_class(name, build, nconf, npcas, D):
     assert torch.equal(Es, E)
 
 
+def test_rff_model_of_another_width_runs_on_the_next_kernel_width():
+    """Upstream accepts any npcas; the kernels exist for 32, 64, 128 and 256.  A 48-component model is evaluated with
+    zero-padded projection matrices and weights: predictions, the scripted forward and the training rows agree with
+    the oracle at the model's own width."""
+    import qml_lightning_b200 as q
+    from oracle import training_rows
+    npcas, D = 48, 384
+    X, Z, c, species = H.batch_mixed(24, seed=31, max_atoms=9)
+    p = H.fchl_params(species)
+    ref = H.rff_model(X, Z, c, p, species, npcas, D)
+    E_ref, F_ref = energy_and_forces(X, Z, c, p, ref, dtype=torch.float64)
+    rep = q.FCHLCuda(species=np.array(species), rcut=p.rcut, nRs2=p.nRs2, nRs3=p.nRs3, eta2=p.eta2, eta3=p.eta3,
+                     two_body_decay=p.two_body_decay, three_body_weight=p.three_body_weight,
+                     three_body_decay=p.three_body_decay, device=DEV)
+    m = q.RandomFourrierFeaturesModel(rep=rep, elements=np.array(species), sigma=2.0, nstacks=D // npcas, npcas=npcas)
+    assert m.reductors.shape[-1] == npcas and m.W.shape[1:] == (npcas, D)
+    m.reductors, m.W, m.b = ref['reductors'].to(DEV), ref['W'].to(DEV), ref['b'].to(DEV)
+    m.set_alpha(ref['alpha'].to(DEV))
+    counts = c.tolist()
+    atomIDs = torch.cat([torch.arange(n, dtype=torch.int32) for n in counts]).to(DEV)
+    molIDs = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, n in enumerate(counts)]).to(DEV)
+    E, F = m.predict_opt(X.to(DEV), Z.to(DEV), atomIDs, molIDs, c.to(DEV))
+    assert ((E.cpu().double() - E_ref).abs() <= H.energy_tolerance(E_ref)).all(), float((E.cpu().double() - E_ref).abs().max())
+    assert (F.cpu().double() - F_ref).abs().max() <= 1e-4
+    scripted = torch.jit.script(m)
+    Xd = X.to(DEV).requires_grad_(True)
+    Es = scripted.forward(Xd, Z.to(DEV), atomIDs, molIDs, c.to(DEV))
+    Fs, = torch.autograd.grad(-Es.sum(), Xd)
+    assert torch.equal(Es.detach(), E) and (Fs - F).abs().max() <= 1e-5
+    Xl = [X[i, :counts[i]].numpy() for i in range(6)]
+    Zl = [Z[i, :counts[i]].numpy() for i in range(6)]
+    data = m.format_data(Xl, Zl)
+    Zt, Gt = m.training_rows(data, with_forces=True)
+    Zr, Gr = training_rows(X[:6], Z[:6], c[:6], p, ref)
+    A = data['charges'].shape[1]
+    assert (Zt.cpu() - Zr).abs().max() <= 2e-6
+    assert (Gt.cpu() - Gr[:, :A]).abs().max() <= 2e-5 * max(1.0, float(Gr.abs().max()))
+    with pytest.raises(ValueError, match='npcas'):
+        q.RandomFourrierFeaturesModel(rep=rep, elements=np.array(species), sigma=2.0, nstacks=2, npcas=320)
+
+
 def test_rff_rejects_unsupported_width():
     from qml_lightning_b200 import cabi
     X, Z, c, species = H.batch_c0(2)
