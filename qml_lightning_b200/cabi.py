@@ -6,6 +6,7 @@ the C entry point of the same name (``qmlb_<name>``).  No arithmetic happens in 
 """
 import ctypes
 import functools
+import os
 
 import torch
 
@@ -620,8 +621,7 @@ def _on_tensor_device(fn):
     """Run ``fn`` with the device of its first CUDA tensor argument current: kernel launches, per-device caches
     inside the library (cuBLAS handle, built-in scratch address) and ``cudaFuncSetAttribute`` all act on the current
     device, which need not be the one the caller's tensors live on."""
-    @functools.wraps(fn)
-    def wrapped(*args, **kwargs):
+    def on_device(*args, **kwargs):
         for a in list(args) + list(kwargs.values()):
             t = a.row_of_slot if isinstance(a, Grouping) else (a.species if isinstance(a, FchlKernelParams) else a)
             if isinstance(t, torch.Tensor) and t.is_cuda:
@@ -630,7 +630,21 @@ def _on_tensor_device(fn):
                 with torch.cuda.device(t.device):
                     return fn(*args, **kwargs)
         return fn(*args, **kwargs)
+
+    @functools.wraps(fn)
+    def wrapped(*args, **kwargs):
+        if not NVTX_RANGES:
+            return on_device(*args, **kwargs)
+        torch.cuda.nvtx.range_push('qmlb200.' + fn.__name__)   # one named range per stage on a profiler's timeline
+        try:
+            return on_device(*args, **kwargs)
+        finally:
+            torch.cuda.nvtx.range_pop()
     return wrapped
+
+
+# Set QMLB200_NVTX=1 (before import) or this flag to wrap every stage of this module in an NVTX range named after it.
+NVTX_RANGES = os.environ.get('QMLB200_NVTX', '0') not in ('', '0')
 
 
 for _name, _fn in list(globals().items()):

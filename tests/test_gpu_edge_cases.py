@@ -139,3 +139,17 @@ def test_row_capacity_too_small_gives_nan_not_wrong_numbers():
     assert bool(bad.any()) and not bool(bad.all()), (int(bad.sum()), total)
     assert torch.equal(torch.isnan(G).flatten(1).any(dim=1), bad)               # the same molecules in the gradient
     assert torch.allclose(E[~bad], E_full[~bad], rtol=0, atol=0) and torch.equal(G[~bad], G_full[~bad])
+
+
+def test_stage_ranges_flag_changes_nothing_but_the_annotation():
+    """With the NVTX flag set every stage wrapper pushes and pops a named range; results are the same bits."""
+    from qml_lightning_b200 import cabi
+    X, Z, c, species = H.batch_c0(4)
+    el = torch.tensor(species, dtype=torch.float32, device=DEV)
+    a = cabi.group_by_element(Z.to(DEV), c.to(DEV), el)
+    cabi.NVTX_RANGES = True
+    try:
+        b = cabi.group_by_element(Z.to(DEV), c.to(DEV), el)
+    finally:
+        cabi.NVTX_RANGES = False
+    assert torch.equal(a.row_of_slot, b.row_of_slot) and torch.equal(a.group_start, b.group_start)
