@@ -8,6 +8,8 @@ and combined with one all-reduce.
 import numpy as np
 import torch
 
+from ..utils.staging import PinnedStage
+
 
 class BaseKernel():
 
@@ -60,25 +62,38 @@ class BaseKernel():
         """
         if self.subtract_self_energies() and self.self_energy is None:
             raise RuntimeError("must call model.calculate_self_energy first - this computes atomic contributions to the potential energy.")
-        dev = self.rep.device
+        dev = torch.device(self.rep.device)
         zbatch = len(X)
-        counts = np.fromiter((x.shape[0] for x in X), dtype=np.int32, count=zbatch)
-        max_atoms = int(counts.max()) if zbatch else 0
-        total = int(counts.sum())
-        mol_ids = np.repeat(np.arange(zbatch, dtype=np.int32), counts)
-        starts = (np.cumsum(counts) - counts).astype(np.int64)
-        atom_ids = (np.arange(total, dtype=np.int64) - np.repeat(starts, counts)).astype(np.int32)
-        coords = np.zeros((zbatch, max_atoms, 3), dtype=np.float32)
-        charges = np.zeros((zbatch, max_atoms), dtype=np.float32)
+        counts_np = np.fromiter((x.shape[0] for x in X), dtype=np.int32, count=zbatch)
+        max_atoms = int(counts_np.max()) if zbatch else 0
+        total = int(counts_np.sum())
+        specs = [((zbatch, max_atoms, 3), np.float32), ((zbatch, max_atoms), np.float32), ((zbatch,), np.int32),
+                 ((total,), np.int32), ((total,), np.int32)]
+        staged = dev.type == 'cuda' and zbatch > 0
+        if staged:       # page-locked staging, copies enqueued without blocking the host (utils/staging.py)
+            if getattr(self, '_stage', None) is None:
+                self._stage = PinnedStage()
+            (coords, charges, counts, atom_ids, mol_ids), pinned = self._stage.arrays(specs)
+        else:
+            coords, charges, counts, atom_ids, mol_ids = (np.zeros(shape, dtype=dt) for shape, dt in specs)
+        counts[:] = counts_np
+        mol_ids[:] = np.repeat(np.arange(zbatch, dtype=np.int32), counts_np)
+        starts = (np.cumsum(counts_np) - counts_np).astype(np.int64)
+        atom_ids[:] = np.arange(total, dtype=np.int64) - np.repeat(starts, counts_np)
         if total:
             coords[mol_ids, atom_ids] = np.concatenate([np.asarray(x, dtype=np.float32).reshape(-1, 3) for x in X])
             charges[mol_ids, atom_ids] = np.concatenate([np.asarray(q, dtype=np.float32).reshape(-1) for q in Q])
+        if staged:
+            d_coords, d_charges, d_counts, d_atom, d_mol = self._stage.upload(pinned, dev)
+        else:
+            d_coords, d_charges, d_counts, d_atom, d_mol = (torch.from_numpy(a).to(dev)
+                                                           for a in (coords, charges, counts, atom_ids, mol_ids))
         data = {
-            'coordinates': torch.from_numpy(coords).to(dev),
-            'charges': torch.from_numpy(charges).to(dev),
-            'natom_counts': torch.from_numpy(counts).to(dev),
-            'atomIDs': torch.from_numpy(atom_ids).to(dev),
-            'molIDs': torch.from_numpy(mol_ids).to(dev),
+            'coordinates': d_coords,
+            'charges': d_charges,
+            'natom_counts': d_counts,
+            'atomIDs': d_atom,
+            'molIDs': d_mol,
             'energies': None,
             'forces': None,
             'cells': torch.empty((0, 3, 3), device=dev),

@@ -153,3 +153,35 @@ def test_stage_ranges_flag_changes_nothing_but_the_annotation():
     finally:
         cabi.NVTX_RANGES = False
     assert torch.equal(a.row_of_slot, b.row_of_slot) and torch.equal(a.group_start, b.group_start)
+
+
+def test_format_data_through_the_pinned_stage_is_reusable():
+    """Two batches formatted back to back share one page-locked staging buffer: the device tensors of the first batch
+    must not change when the second overwrites the stage, and both must equal a plain host construction."""
+    import qml_lightning_b200 as q
+    from tests.test_gpu_models import build_model
+    X, Z, c, species = H.batch_mixed(40, seed=5, max_atoms=12)
+    _, _, m = build_model(X[:8], Z[:8], c[:8], species, 32, 2)
+    counts = c.tolist()
+    Xl = [X[i, :counts[i]].numpy() for i in range(40)]
+    Zl = [Z[i, :counts[i]].numpy() for i in range(40)]
+
+    def plain(lo, hi):
+        A = max(counts[lo:hi])
+        co = torch.zeros(hi - lo, A, 3)
+        ch = torch.zeros(hi - lo, A)
+        for i in range(lo, hi):
+            co[i - lo, :counts[i]] = X[i, :counts[i]]
+            ch[i - lo, :counts[i]] = Z[i, :counts[i]]
+        atom = torch.cat([torch.arange(n, dtype=torch.int32) for n in counts[lo:hi]])
+        mol = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, n in enumerate(counts[lo:hi])])
+        return co, ch, torch.tensor(counts[lo:hi], dtype=torch.int32), atom, mol
+
+    first = m.format_data(Xl[:30], Zl[:30])
+    second = m.format_data(Xl[30:], Zl[30:])
+    torch.cuda.synchronize()
+    for data, ref in ((first, plain(0, 30)), (second, plain(30, 40))):
+        for key, want in zip(('coordinates', 'charges', 'natom_counts', 'atomIDs', 'molIDs'), ref):
+            got = data[key].cpu()
+            assert got.dtype == want.dtype and torch.equal(got, want), key
+    assert m._stage.buffer.is_pinned()
