@@ -23,6 +23,7 @@
 
 #include "common.cuh"
 #include "fwht_tile.cuh"
+#include "sincos.cuh"
 
 namespace {
 
@@ -227,8 +228,7 @@ sorf_energy_grad_kernel(const float *__restrict__ x, const int *__restrict__ gro
                             __sincosf(arg.x, &sn.x, &cs.x);
                             __sincosf(arg.y, &sn.y, &cs.y);
                         } else {
-                            sincosf(arg.x, &sn.x, &cs.x);
-                            sincosf(arg.y, &sn.y, &cs.y);
+                            qmlb_sincos::sincos_pair(arg, sn, cs);
                         }
                         eacc2[a] = __ffma2_rn(make_float2(aa[r], aa[r + 1]), cs, eacc2[a]);
                         const float2 gq = __fmul2_rn(make_float2(-aa[r], -aa[r + 1]), sn);
@@ -417,8 +417,7 @@ sorf_pair_kernel(const float *__restrict__ x, const int *__restrict__ group_star
                         __sincosf(arg.x, &sn.x, &cs.x);
                         __sincosf(arg.y, &sn.y, &cs.y);
                     } else {
-                        sincosf(arg.x, &sn.x, &cs.x);
-                        sincosf(arg.y, &sn.y, &cs.y);
+                        qmlb_sincos::sincos_pair(arg, sn, cs);
                     }
                     const float2 a2 = make_float2(aa[r], aa[r]);
                     eacc = __ffma2_rn(a2, cs, eacc);
@@ -535,7 +534,7 @@ int launch_fused(const float *x, const int *group_start, const int *slot_of_row,
         sorf_energy_grad_kernel<LOG2N, FASTV, TTV, AT><<<grid, WARPS * 32, smem, st>>>(                               \
             x, group_start, slot_of_row, nel, S, T, scale, Dp, bp, ap, atom_energy, grad_x);                           \
     } while (0)
-    if (T == 1 && fast && LOG2N >= 6 && LOG2N <= 8 && SORF_PAIR) {   // accurate sincosf: the per-atom kernel is faster (26.6 against 33.3 ms on c1)
+    if (T == 1 && LOG2N >= 6 && LOG2N <= 8 && SORF_PAIR) {
         constexpr int PL = (LOG2N >= 6 && LOG2N <= 8) ? LOG2N : 8;   // keeps the other instantiations well formed
         const size_t smem = sizeof(float) * WARPS * PairCfg<PL>::WARP_FLOATS;
         const unsigned grid = (unsigned)((rows_cap + WARPS * 2 - 1) / (WARPS * 2));
