@@ -252,6 +252,48 @@ def test_fused_sorf_energy_grad(cabi, N, T, fast):
         assert (e_atom[r0:r1][~live] == 0).all()
 
 
+@pytest.mark.parametrize('N', [32, 128, 256])
+@pytest.mark.parametrize('log2_scale,bias_step', [(5, 1.0 / 256), (12, 1.0)])
+def test_accurate_sin_cos_on_exactly_representable_large_arguments(cabi, N, log2_scale, bias_step):
+    """fast_math=False evaluates sin/cos in float32 without the SFU.  Integer-valued inputs, sign diagonals of +-1, a
+    power-of-two scale and a bias on a binary grid make every argument scale*u + b exact in float32, so the only error
+    left is the sin/cos evaluation itself: arguments up to 2.5e4 (scale 32: the branch-free reduction) and up to 3e6
+    (scale 4096: mostly the large-argument path, the small transforms still on the branch-free one)."""
+    X, Z, c, species = H.batch_mixed(10, seed=N)
+    nel, S, T = len(species), 6, 1
+    sigma = 2.0 ** -log2_scale
+    el = torch.tensor(species, dtype=torch.float32, device=DEV)
+    g = cabi.group_by_element(Z.to(DEV), c.to(DEV), el)
+    gen = torch.Generator().manual_seed(N + log2_scale)
+    x = torch.randint(-3, 4, (g.rows_cap, N), generator=gen).float()
+    D = torch.randint(0, 2, (nel, T, S, N), generator=gen).float() * 2 - 1
+    bias = torch.randint(0, int(6 / bias_step), (nel, S * N), generator=gen).float() * bias_step
+    alpha = torch.randn(S * N, generator=gen)
+    packed = cabi.sorf_pack(D.to(DEV), bias.to(DEV), alpha.to(DEV))
+    e_atom, gx = cabi.sorf_energy_grad(x.to(DEV), g, packed, N, S, T, sigma, fast_math=False)
+    e_atom, gx = e_atom.cpu().double(), gx.cpu().double()
+    gs, sor = g.group_start.cpu(), g.slot_of_row.cpu()
+    F = S * N
+    largest = 0.0
+    for ei in range(nel):
+        r0, r1 = int(gs[ei]), int(gs[ei + 1])
+        if r1 == r0:
+            continue
+        xs = x[r0:r1].double().clone().requires_grad_(True)
+        cf = sorf_coefficients(xs, D[ei], math.sqrt(N) / sigma, T).reshape(-1, F)
+        arg = cf + bias[ei].double()
+        snap = (arg.detach().float().double() - arg.detach())                 # sqrt(N) / sqrt(N) leaves 1e-16 relative noise
+        assert snap.abs().max() <= 1e-9                                        # ... on arguments that are exact in float32
+        arg = arg + snap
+        largest = max(largest, float(arg.abs().max()))
+        e_ref = (math.sqrt(2.0 / F) * torch.cos(arg) * alpha.double()).sum(-1)
+        g_ref, = torch.autograd.grad(e_ref.sum(), xs)
+        live = sor[r0:r1] >= 0
+        assert (e_atom[r0:r1][live] - e_ref.detach()[live]).abs().max() <= 5e-6 * max(1.0, float(e_ref.abs().max()))
+        assert (gx[r0:r1][live] - g_ref[live]).abs().max() <= 5e-6 * max(1.0, float(g_ref.abs().max()))
+    assert largest > (1e5 if log2_scale == 12 else 1e3)
+
+
 @pytest.mark.parametrize('repsize,npcas', [(336, 256), (780, 128), (100, 32), (336, 512), (72, 16), (130, 48)])
 def test_pca_project_packed_matches_float64(repsize, npcas):
     """The pipeline's projection kernel (pre-split projection matrices, up to 256 columns per block, bulk-copied B
