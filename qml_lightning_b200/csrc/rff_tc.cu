@@ -15,7 +15,7 @@
 //     image: 8x8 fp16 core matrices [8 k][8 features], blocks ordered (feature block, k block), hi image then lo image,
 //     then the chunk's bias and weights.  The same image is the B operand of the first product (MN-major: N = features)
 //     and of the second (K-major: N = k, K = features), so a chunk is fetched once, by one cp.async.bulk of 32.4 KB
-//     issued by a producer thread into a ring of three stages, and used twice;
+//     issued by a producer thread into a ring of four stages, and used twice;
 //   * first product, per chunk: x_hi [W_hi | W_lo] as npcas/16 MMAs with N = 64 (the lo image continues the hi image at
 //     the feature-block stride, so one descriptor covers both) and x_lo W_hi as npcas/16 MMAs with N = 32, into one of
 //     two 64-column tensor-memory buffers [hi*hi | cross terms].  Measured: an MMA occupies the tensor pipe for
@@ -34,7 +34,14 @@
 // 1.9e-6 at 16 chunks, 3.5e-6 at 32, 5.5e-5 without folding over 512 chunks).
 //
 // Tensor memory (all 512 columns): arg 2 x 64, gradient npcas (<= 256), x_hi npcas/2 (<= 128).
-// Shared memory at npcas = 256: x_lo 64 KB, weight ring 3 x 32.4 KB, G 2 x 16 KB.
+// Shared memory at npcas = 256: x_lo 64 KB, weight ring 4 x 32.4 KB, G 16 KB, fold staging 12 KB.
+//
+// The block is a pipeline of stages that wait on one another (weight copy -> first product -> sin/cos -> second product
+// -> stage free), and its period is set by the longest of these loops, not by the tensor pipe (about 55 % busy).  Cycle
+// counters around every wait showed the loop through the weight ring to be the longest with three stages: the copy of
+// chunk c+3 can only start when the second product of chunk c has released its stage.  The ring therefore has four
+// stages, paid for with a single G image instead of two (the sin/cos warps wait for the second product of the previous
+// chunk before they store, which is off the critical loop); 106.5 -> 95.9 ms on 2.1 M rows x 16,384 features.
 //
 // Every wait is bounded.  A thread that times out marks the block as failed; the block then skips its stores, waits
 // (bounded) for its copies and MMAs in flight, releases its tensor memory and counts the event (qmlb_tc_timeouts).
@@ -54,11 +61,23 @@ constexpr int FC = 32;             // features per chunk
 constexpr int EPI_WARPS = 8;       // warps 0-7: sin/cos + flush (warps w and w+4 share the rows of a tensor-memory lane quarter)
 constexpr int MMA_WARP = 8;        // warp 8: MMAs of the first product for even chunks (+ tensor-memory allocation), warp 9: MMAs
 constexpr int NTHREADS = 384;      // of the second product, warp 10: weight copies, warp 11: first product for odd chunks
-constexpr int NSTAGES = 3;         // weight chunks in flight
+#ifndef QMLB_RFF_STAGES
+#define QMLB_RFF_STAGES 4
+#endif
+#ifndef QMLB_RFF_GBUFS
+#define QMLB_RFF_GBUFS 1
+#endif
+#ifndef QMLB_RFF_FOLD_STAGE
+#define QMLB_RFF_FOLD_STAGE 1
+#endif
+constexpr int NSTAGES = QMLB_RFF_STAGES;   // weight chunks in flight
+constexpr int G_BUFS = QMLB_RFF_GBUFS;     // G images in flight between the sin/cos warps and the second product
 #ifndef QMLB_RFF_FLUSH_CHUNKS
 #define QMLB_RFF_FLUSH_CHUNKS 16
 #endif
 constexpr int FLUSH_CHUNKS = QMLB_RFF_FLUSH_CHUNKS;  // gradient accumulator folded into global memory every this many chunks
+constexpr int FOLD_STRIDE = 12;     // floats per row of the fold's staging slab (8 + 4: conflict-free 128-bit row stores)
+constexpr int FLUSH_DELAY = G_BUFS;   // ... this many chunks after the group's last chunk (as many as there are G buffers)
 constexpr int WAIT_LIMIT = 1 << 22;
 constexpr size_t HEADER_BYTES = 256;
 constexpr int EXP_CLAMP = 40;
@@ -265,7 +284,7 @@ __global__ void rff_pack_header_kernel(PackHeader *hdr, int K, int D, int nchunk
 // barrier slots
 enum {
     W_FULL = 0, W_FREE = W_FULL + NSTAGES, ARG_FULL = W_FREE + NSTAGES, ARG_FREE = ARG_FULL + 2, G_FULL = ARG_FREE + 2,
-    G_FREE = G_FULL + 2, GRAD_FULL = G_FREE + 2, GRAD_FREE, ALL_DONE, NBARS
+    G_FREE = G_FULL + G_BUFS, GRAD_FULL = G_FREE + G_BUFS, GRAD_FREE, ALL_DONE, NBARS
 };
 
 // tensor-memory columns (512 allocated)
@@ -281,7 +300,9 @@ struct Smem {
     static constexpr uint32_t CHUNK = (uint32_t)chunk_bytes(K);
     static constexpr uint32_t G_HALF = BM * FC * 2;             // G hi (or lo) image
     static constexpr uint32_t OFF_XL = 0, OFF_W = X_HALF, OFF_G = OFF_W + NSTAGES * CHUNK;
-    static constexpr uint32_t TOTAL = OFF_G + 4 * G_HALF;
+    static constexpr uint32_t OFF_FOLD = OFF_G + 2 * G_BUFS * G_HALF;   // staging slabs of the gradient fold, one per sin/cos warp
+    static constexpr uint32_t FOLD_WARP = 32 * FOLD_STRIDE * 4;
+    static constexpr uint32_t TOTAL = OFF_FOLD + (QMLB_RFF_FOLD_STAGE ? EPI_WARPS * FOLD_WARP : 0);
     static_assert(CHUNK % 128 == 0, "chunk images must keep 128-byte alignment");
 };
 
@@ -335,10 +356,8 @@ rff_tc_kernel(const float *__restrict__ x, const int *__restrict__ group_start, 
 
     if (tid == 0) {
         for (int i = 0; i < NSTAGES; ++i) { mbar_init(bar(W_FULL + i), 1); mbar_init(bar(W_FREE + i), 1); }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(bar(ARG_FULL + i), 1); mbar_init(bar(ARG_FREE + i), EPI_WARPS);
-            mbar_init(bar(G_FULL + i), EPI_WARPS); mbar_init(bar(G_FREE + i), 1);
-        }
+        for (int i = 0; i < 2; ++i) { mbar_init(bar(ARG_FULL + i), 1); mbar_init(bar(ARG_FREE + i), EPI_WARPS); }
+        for (int i = 0; i < G_BUFS; ++i) { mbar_init(bar(G_FULL + i), EPI_WARPS); mbar_init(bar(G_FREE + i), 1); }
         mbar_init(bar(GRAD_FULL), 1); mbar_init(bar(GRAD_FREE), EPI_WARPS); mbar_init(bar(ALL_DONE), 3);
         failed = 0;
         xmax_bits = 0u;
@@ -433,8 +452,11 @@ rff_tc_kernel(const float *__restrict__ x, const int *__restrict__ group_start, 
         const uint32_t lane_field = (uint32_t)((warp & 3) * 32) << 16;
         float eacc = 0.f, ecomp = 0.f;  // energy of the row, summed over the chunks with compensation
         bool ok = tmem_ok;
+        int next_fold = 0;
+        const int last_group = (nchunks - 1) / FLUSH_CHUNKS;
+        const unsigned live_rows = __ballot_sync(QMLB_FULL_MASK, live);
         for (int c = 0; c < nchunks && ok; ++c) {
-            const int b = c & 1, s = c % NSTAGES;
+            const int b = c & 1, s = c % NSTAGES, gb = c % G_BUFS;
             const uint32_t par = (uint32_t)(c >> 1) & 1u;
             if (!mbar_wait(bar(ARG_FULL + b), par)) { ok = false; break; }
             fence_after();
@@ -470,9 +492,9 @@ rff_tc_kernel(const float *__restrict__ x, const int *__restrict__ group_start, 
                 glo[q] = *reinterpret_cast<uint32_t *>(&lo);
             }
             // the previous use of this G buffer (chunk c-2) must have been consumed by its MMAs
-            if (c >= 2 && !mbar_wait(bar(G_FREE + b), (uint32_t)((c >> 1) - 1) & 1u)) { ok = false; break; }
+            if (c >= G_BUFS && !mbar_wait(bar(G_FREE + gb), (uint32_t)((c / G_BUFS) - 1) & 1u)) { ok = false; break; }
             {   // canonical K-major image (K = features): 8 rows x 8 features per 128-byte core matrix, feature blocks outermost
-                unsigned char *gbuf = sptr + S::OFF_G + b * 2 * S::G_HALF;
+                unsigned char *gbuf = sptr + S::OFF_G + gb * 2 * S::G_HALF;
                 const uint32_t off = (uint32_t)(2 * h) * 2048u + (uint32_t)(r >> 3) * 128u + (uint32_t)(r & 7) * 16u;
                 *reinterpret_cast<uint4 *>(gbuf + off) = make_uint4(ghi[0], ghi[1], ghi[2], ghi[3]);
                 *reinterpret_cast<uint4 *>(gbuf + off + 2048u) = make_uint4(ghi[4], ghi[5], ghi[6], ghi[7]);
@@ -481,18 +503,53 @@ rff_tc_kernel(const float *__restrict__ x, const int *__restrict__ group_start, 
             }
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(G_FULL + b));
+            if (lane == 0) mbar_arrive(bar(G_FULL + gb));
             {   // Kahan step: a plain running sum over nfeatures terms would lose ~sqrt(nfeatures) ulps
                 const float y = echunk - ecomp, t = eacc + y;
                 ecomp = (t - eacc) - y;
                 eacc = t;
             }
 
-            if ((c % FLUSH_CHUNKS) == FLUSH_CHUNKS - 1 || c == nchunks - 1) {
-                // fold the gradient accumulator of this group into global memory
-                const int group = c / FLUSH_CHUNKS;
-                if (!mbar_wait(bar(GRAD_FULL), (uint32_t)group & 1u)) { ok = false; break; }
+            // Fold finished accumulator groups into global memory.  A group ends at chunk E = min(FLUSH_CHUNKS (g+1), nchunks) - 1;
+            // it is folded FLUSH_DELAY chunks later (at the last chunk if that comes first): by then its last MMAs have
+            // left the pipe, so the wait below is short, and the first product already runs ahead on the next chunks
+            // while this warp reads the accumulator, instead of the whole pipeline draining at every fold.
+            while (ok && next_fold <= last_group) {
+                const int group_end = min((next_fold + 1) * FLUSH_CHUNKS, nchunks) - 1;
+                if (c != nchunks - 1 && c < group_end + FLUSH_DELAY) break;
+                if (!mbar_wait(bar(GRAD_FULL), (uint32_t)next_fold & 1u)) { ok = false; break; }
                 fence_after();
+#if QMLB_RFF_FOLD_STAGE
+                // The accumulator arrives one row per thread; adding it from there would send 32 separate 16-byte
+                // atomics (rows are K floats apart) per instruction.  The warp's tile goes through a staging slab
+                // instead, eight columns at a time, so that two lanes cover a whole 32-byte sector of a row.
+                float *stg = reinterpret_cast<float *>(sptr + S::OFF_FOLD + warp * S::FOLD_WARP);
+#pragma unroll 1
+                for (int cc = 0; cc < K / 2; cc += 16) {
+                    uint32_t v0[16];
+                    tmem_ld16(tmem + lane_field + COL_GRAD + (uint32_t)(h * (K / 2) + cc), v0);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        float4 *own = reinterpret_cast<float4 *>(stg + lane * FOLD_STRIDE);
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            const int e = 8 * half + 4 * q;
+                            own[q] = make_float4(__uint_as_float(v0[e]) * grad_scale, __uint_as_float(v0[e + 1]) * grad_scale,
+                                                 __uint_as_float(v0[e + 2]) * grad_scale, __uint_as_float(v0[e + 3]) * grad_scale);
+                        }
+                        __syncwarp();
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            const int rr = 16 * j + (lane >> 1), c4 = (lane & 1) * 4;
+                            const float4 t = *reinterpret_cast<const float4 *>(stg + rr * FOLD_STRIDE + c4);
+                            if ((live_rows >> rr) & 1u)   // rows of the padding keep their zeros
+                                red_add4(grad_x + (size_t)(row0 + (warp & 3) * 32 + rr) * K + h * (K / 2) + cc + 8 * half + c4, t.x, t.y, t.z, t.w);
+                        }
+                        __syncwarp();
+                    }
+                }
+#else
                 float *dst = grad_x + (size_t)(row0 + r) * K + h * (K / 2);
 #pragma unroll 1
                 for (int cc = 0; cc < K / 2; cc += 16) {
@@ -506,9 +563,11 @@ rff_tc_kernel(const float *__restrict__ x, const int *__restrict__ group_start, 
                                      __uint_as_float(v0[4 * q + 2]) * grad_scale, __uint_as_float(v0[4 * q + 3]) * grad_scale);
                     }
                 }
+#endif
                 fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(GRAD_FREE));
+                ++next_fold;
             }
         }
         if (!ok) failed = 1;  // benign race: every writer stores 1
@@ -569,15 +628,15 @@ rff_tc_kernel(const float *__restrict__ x, const int *__restrict__ group_start, 
         constexpr uint32_t grad = tmem + COL_GRAD;
         bool ok = tmem_ok;
         for (int c = 0; c < nchunks && ok; ++c) {
-            const int s = c % NSTAGES, b = c & 1;
+            const int s = c % NSTAGES, gb = c % G_BUFS;
             const int group = c / FLUSH_CHUNKS;
             const bool first = (c % FLUSH_CHUNKS) == 0;
-            bool w = mbar_wait(bar(G_FULL + b), (uint32_t)(c >> 1) & 1u);
+            bool w = mbar_wait(bar(G_FULL + gb), (uint32_t)(c / G_BUFS) & 1u);
             if (first && group > 0) w = mbar_wait(bar(GRAD_FREE), (uint32_t)(group - 1) & 1u) && w;
             if (!__all_sync(QMLB_FULL_MASK, w)) { ok = false; break; }
             fence_after();
             const uint32_t wh_lo = desc_lo(sbase + S::OFF_W + s * S::CHUNK, (uint32_t)KB * 128u), wl_lo = wh_lo + (S::W_HALF >> 4);
-            const uint32_t gh_lo = desc_lo(sbase + S::OFF_G + b * 2 * S::G_HALF, 2048u), gl_lo = gh_lo + (S::G_HALF >> 4);
+            const uint32_t gh_lo = desc_lo(sbase + S::OFF_G + gb * 2 * S::G_HALF, 2048u), gl_lo = gh_lo + (S::G_HALF >> 4);
             if (lane == 0) {
 #pragma unroll
                 for (int ks = 0; ks < FC / 16; ++ks) {
@@ -587,7 +646,7 @@ rff_tc_kernel(const float *__restrict__ x, const int *__restrict__ group_start, 
                     mma_ss(grad, gh_lo + ks * 256, ab_hi, wh_lo + step, ab_hi, idesc2, 1u);
                 }
                 mma_commit(bar(W_FREE + s));
-                mma_commit(bar(G_FREE + b));
+                mma_commit(bar(G_FREE + gb));
                 if ((c % FLUSH_CHUNKS) == FLUSH_CHUNKS - 1 || c == nchunks - 1) mma_commit(bar(GRAD_FULL));
             }
             __syncwarp();
