@@ -182,10 +182,13 @@ __device__ __forceinline__ void poison_tile(float *out, int row0, int tile, cons
     }
 }
 
-enum { A_FULL = 0, B_FULL = A_FULL + NSTAGES, STAGE_FREE = B_FULL + NSTAGES, ACC_FULL = STAGE_FREE + NSTAGES, ACC_FREE, ALL_DONE, NBARS };
+enum { A_FULL = 0, B_FULL = A_FULL + NSTAGES, STAGE_FREE = B_FULL + NSTAGES, ACC_FULL = STAGE_FREE + NSTAGES, ACC_FREE = ACC_FULL + 2, ALL_DONE = ACC_FREE + 2, NBARS };
 
 // 10 warps = 3 per SM sub-partition at most, whose 16,384 registers allow 168 per thread; the register row of the drain
 // (128 floats, touched once per group) is what spills.
+// NTM = widest tile the instantiation serves (128 or 256 columns).  The narrow one keeps half the register row, which
+// leaves room for twice as many tensor-memory loads in flight during a fold, and two accumulator sets.
+template <int NTM>
 __global__ void __launch_bounds__(NTHREADS, 1)
 pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ packed, const int *__restrict__ group_start, int nel,
                Tiling t, int group_chunks, float *__restrict__ out, unsigned launch_seq) {
@@ -216,7 +219,8 @@ pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ p
         for (int s = 0; s < NSTAGES; ++s) {
             mbar_init(bar(A_FULL + s), WORKER_WARPS); mbar_init(bar(B_FULL + s), 1); mbar_init(bar(STAGE_FREE + s), 1);
         }
-        mbar_init(bar(ACC_FULL), 1); mbar_init(bar(ACC_FREE), WORKER_WARPS); mbar_init(bar(ALL_DONE), 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(bar(ACC_FULL + i), 1); mbar_init(bar(ACC_FREE + i), WORKER_WARPS); }
+        mbar_init(bar(ALL_DONE), 1);
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -231,6 +235,9 @@ pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ p
     const uint32_t tmem_alloc = tmem_slot;
     constexpr uint32_t tmem = 0u;
     const bool tmem_ok = tmem_alloc == 0u;
+    // Tiles of at most 128 columns leave room for two accumulator sets (main and cross-term columns each): the MMAs of a
+    // group then run into one set while the worker warps fold the other, instead of the two taking turns.
+    const int nbuf = NT <= 128 ? 2 : 1;
 
     if (warp < WORKER_WARPS) {
         // ------------------------------------------------------------------ A staging + accumulator drain
@@ -240,9 +247,9 @@ pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ p
         const int half = NT / 2;
         const float *src = in + (size_t)(row0 + r) * K;
         const bool vec = (K & 3) == 0;
-        float racc[NT_MAX / 2];
+        float racc[NTM / 2];
 #pragma unroll
-        for (int i = 0; i < NT_MAX / 2; ++i) racc[i] = 0.f;
+        for (int i = 0; i < NTM / 2; ++i) racc[i] = 0.f;
         float4 pre[4];
         auto fetch = [&](int c) {
 #pragma unroll
@@ -259,23 +266,28 @@ pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ p
         };
         // fold the accumulators of group g into the register row
         auto drain = [&](int g) {
-            if (!mbar_wait(bar(ACC_FULL), (uint32_t)g & 1u)) return false;
+            const int buf = g % nbuf;
+            if (!mbar_wait(bar(ACC_FULL + buf), (uint32_t)(g / nbuf) & 1u)) return false;
             fence_after();
-            const uint32_t base = tmem + lane_field + (uint32_t)(h * half);
+            const uint32_t base = tmem + lane_field + (uint32_t)(h * half + buf * 128);
+            constexpr int STEP = NTM <= 128 ? 16 : 8;     // columns per round trip to tensor memory
 #pragma unroll
-            for (int cc = 0; cc < NT_MAX / 2; cc += 8) {
+            for (int cc = 0; cc < NTM / 2; cc += STEP) {
                 if (cc < half) {
-                    uint32_t m[8], x[8];
-                    tmem_ld8(base + COL_MAIN + (uint32_t)cc, m);
-                    tmem_ld8(base + COL_CROSS + (uint32_t)cc, x);
+                    uint32_t m[STEP], x[STEP];
+#pragma unroll
+                    for (int q = 0; q < STEP; q += 8) {
+                        tmem_ld8(base + COL_MAIN + (uint32_t)(cc + q), reinterpret_cast<uint32_t(&)[8]>(m[q]));
+                        tmem_ld8(base + COL_CROSS + (uint32_t)(cc + q), reinterpret_cast<uint32_t(&)[8]>(x[q]));
+                    }
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) racc[cc + i] += __uint_as_float(m[i]) + __uint_as_float(x[i]);
+                    for (int i = 0; i < STEP; ++i) racc[cc + i] += __uint_as_float(m[i]) + __uint_as_float(x[i]);
                 }
             }
             fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(ACC_FREE));
+            if (lane == 0) mbar_arrive(bar(ACC_FREE + buf));
             return true;
         };
         bool ok = tmem_ok;
@@ -311,7 +323,7 @@ pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ p
             const int col0 = tile * NT + h * half;
             const bool vec_out = (t.Nout & 3) == 0 && (half & 3) == 0;
 #pragma unroll
-            for (int cc = 0; cc < NT_MAX / 2; cc += 4) {
+            for (int cc = 0; cc < NTM / 2; cc += 4) {
                 if (cc < half) {
                     if (vec_out && col0 + cc + 3 < t.Nout) {
                         *reinterpret_cast<float4 *>(dst + cc) = make_float4(racc[cc], racc[cc + 1], racc[cc + 2], racc[cc + 3]);
@@ -339,7 +351,8 @@ pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ p
             const bool first = (c % group_chunks) == 0;
             bool w = mbar_wait(bar(A_FULL + s), par, c == 0 ? QMLB_TEST_FIRST_WAIT_POLLS : WAIT_LIMIT);
             w = w && mbar_wait(bar(B_FULL + s), par);
-            if (first && g > 0) w = mbar_wait(bar(ACC_FREE), (uint32_t)(g - 1) & 1u) && w;
+            const int buf = g % nbuf;
+            if (first && g >= nbuf) w = mbar_wait(bar(ACC_FREE + buf), (uint32_t)((g / nbuf) - 1) & 1u) && w;
             if (!__all_sync(QMLB_FULL_MASK, w)) { ok = false; break; }
             fence_after();
             const uint32_t a_base = sbase + (uint32_t)s * stage_bytes, b_base = a_base + 2 * A_HALF;
@@ -350,12 +363,13 @@ pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ p
 #pragma unroll
                 for (int j = 0; j < BK / 8; ++j) {
                     const uint32_t acc = (first && j == 0) ? 0u : 1u;
-                    mma_tf32(tmem + COL_CROSS, ah + j * 256, ab_hi, bl + j * b_step, ab_hi, idesc, acc);
-                    mma_tf32(tmem + COL_CROSS, al + j * 256, ab_hi, bh + j * b_step, ab_hi, idesc, 1u);
-                    mma_tf32(tmem + COL_MAIN, ah + j * 256, ab_hi, bh + j * b_step, ab_hi, idesc, acc);
+                    const uint32_t set = (uint32_t)(buf * 128);
+                    mma_tf32(tmem + COL_CROSS + set, ah + j * 256, ab_hi, bl + j * b_step, ab_hi, idesc, acc);
+                    mma_tf32(tmem + COL_CROSS + set, al + j * 256, ab_hi, bh + j * b_step, ab_hi, idesc, 1u);
+                    mma_tf32(tmem + COL_MAIN + set, ah + j * 256, ab_hi, bh + j * b_step, ab_hi, idesc, acc);
                 }
                 mma_commit(bar(STAGE_FREE + s));
-                if ((c % group_chunks) == group_chunks - 1 || c == nchunks - 1) mma_commit(bar(ACC_FULL));
+                if ((c % group_chunks) == group_chunks - 1 || c == nchunks - 1) mma_commit(bar(ACC_FULL + buf));
             }
             __syncwarp();
         }
@@ -436,13 +450,20 @@ extern "C" int qmlb_pca_project_packed(const float *in, const void *packed, cons
     if (rows_cap == 0) return QMLB_OK;
     const Tiling t = make_tiling(repsize, npcas, transpose);
     const size_t smem = (size_t)NSTAGES * (2 * A_HALF + t.chunk_bytes) + 128;
-    if (int rc = qmlb::ensure_smem(pca_tc2_kernel, smem, "qmlb_pca_project_packed")) return rc;
+    const bool narrow = t.NT <= 128;
+    if (int rc = narrow ? qmlb::ensure_smem(pca_tc2_kernel<128>, smem, "qmlb_pca_project_packed")
+                        : qmlb::ensure_smem(pca_tc2_kernel<NT_MAX>, smem, "qmlb_pca_project_packed"))
+        return rc;
     // projection: fold every chunk (32 k); transposed product (K = npcas): fold once per 8 chunks
     const int group_chunks = transpose ? 8 : 1;
     dim3 grid((unsigned)(rows_cap / BM), (unsigned)t.ntiles);
     static std::atomic<unsigned> launches{0};
     const unsigned seq = ++launches;   // never 0, the initial value of the device-side marker
-    pca_tc2_kernel<<<grid, NTHREADS, smem, qmlb::as_stream(stream)>>>(in, static_cast<const unsigned char *>(packed), group_start,
-                                                                      nelements, t, group_chunks, out, seq);
+    if (narrow)
+        pca_tc2_kernel<128><<<grid, NTHREADS, smem, qmlb::as_stream(stream)>>>(in, static_cast<const unsigned char *>(packed), group_start,
+                                                                               nelements, t, group_chunks, out, seq);
+    else
+        pca_tc2_kernel<NT_MAX><<<grid, NTHREADS, smem, qmlb::as_stream(stream)>>>(in, static_cast<const unsigned char *>(packed), group_start,
+                                                                                  nelements, t, group_chunks, out, seq);
     return qmlb::check_launch("qmlb_pca_project_packed");
 }
