@@ -13,7 +13,8 @@
 //   * eight worker warps stage the A chunks (one row half-chunk per thread) and drain the accumulators, one warp
 //     issues the MMAs, one warp issues the copies; two stages of (A 32 KB + B up to 64 KB).
 // The tensor core adds into its fp32 accumulator with truncation towards zero, which biases long accumulations.  The
-// small cross terms (hi*lo, lo*hi) therefore have their own accumulator columns, and the accumulators are folded into
+// small cross terms (hi*lo, lo*hi) therefore have their own accumulator columns, which run over the whole K and are read
+// once at the end (at 2^-11 of the main term their truncation does not matter), and the hi*hi accumulator is folded into
 // fp32 registers every `group_chunks` chunks: 1 (32 k, 4 truncating adds of hi*hi terms) for the projection, whose
 // result feeds cos() -- measured on a 21-atom model with weights of magnitude 10^3, the projected rows are then
 // 3.0e-7 from float64 (relative to their maximum; an fp32 FFMA loop: 4.4e-7; folding every 3 chunks: 1.25e-6, which
@@ -265,24 +266,36 @@ pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ p
             }
         };
         // fold the accumulators of group g into the register row
-        auto drain = [&](int g) {
+        // (the cross-term columns are small, so they accumulate over the whole K and are read once, with the last group)
+        auto drain = [&](int g, bool with_cross) {
             const int buf = g % nbuf;
             if (!mbar_wait(bar(ACC_FULL + buf), (uint32_t)(g / nbuf) & 1u)) return false;
             fence_after();
             const uint32_t base = tmem + lane_field + (uint32_t)(h * half + buf * 128);
-            constexpr int STEP = NTM <= 128 ? 16 : 8;     // columns per round trip to tensor memory
+            constexpr int STEP = 16;     // columns per round trip to tensor memory
 #pragma unroll
             for (int cc = 0; cc < NTM / 2; cc += STEP) {
                 if (cc < half) {
-                    uint32_t m[STEP], x[STEP];
+                    uint32_t m[STEP];
 #pragma unroll
-                    for (int q = 0; q < STEP; q += 8) {
-                        tmem_ld8(base + COL_MAIN + (uint32_t)(cc + q), reinterpret_cast<uint32_t(&)[8]>(m[q]));
-                        tmem_ld8(base + COL_CROSS + (uint32_t)(cc + q), reinterpret_cast<uint32_t(&)[8]>(x[q]));
-                    }
+                    for (int q = 0; q < STEP; q += 8) tmem_ld8(base + COL_MAIN + (uint32_t)(cc + q), reinterpret_cast<uint32_t(&)[8]>(m[q]));
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < STEP; ++i) racc[cc + i] += __uint_as_float(m[i]) + __uint_as_float(x[i]);
+                    for (int i = 0; i < STEP; ++i) racc[cc + i] += __uint_as_float(m[i]);
+                }
+            }
+            if (with_cross) {
+                const uint32_t xbase = tmem + lane_field + (uint32_t)(h * half) + COL_CROSS;
+#pragma unroll
+                for (int cc = 0; cc < NTM / 2; cc += STEP) {
+                    if (cc < half) {
+                        uint32_t x[STEP];
+#pragma unroll
+                        for (int q = 0; q < STEP; q += 8) tmem_ld8(xbase + (uint32_t)(cc + q), reinterpret_cast<uint32_t(&)[8]>(x[q]));
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < STEP; ++i) racc[cc + i] += __uint_as_float(x[i]);
+                    }
                 }
             }
             fence_before();
@@ -315,9 +328,9 @@ pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ p
 
             // the group that ended with the previous chunk is folded now, after this chunk has been staged, so that the
             // staging overlaps the group's last MMAs
-            if (c >= 1 && ((c - 1) % group_chunks) == group_chunks - 1) ok = drain((c - 1) / group_chunks);
+            if (c >= 1 && ((c - 1) % group_chunks) == group_chunks - 1) ok = drain((c - 1) / group_chunks, false);
         }
-        if (ok) ok = drain((nchunks - 1) / group_chunks);
+        if (ok) ok = drain((nchunks - 1) / group_chunks, true);
         if (ok) {
             float *dst = out + (size_t)(row0 + r) * t.Nout + (size_t)tile * NT + h * half;
             const int col0 = tile * NT + h * half;
@@ -364,8 +377,8 @@ pca_tc2_kernel(const float *__restrict__ in, const unsigned char *__restrict__ p
                 for (int j = 0; j < BK / 8; ++j) {
                     const uint32_t acc = (first && j == 0) ? 0u : 1u;
                     const uint32_t set = (uint32_t)(buf * 128);
-                    mma_tf32(tmem + COL_CROSS + set, ah + j * 256, ab_hi, bl + j * b_step, ab_hi, idesc, acc);
-                    mma_tf32(tmem + COL_CROSS + set, al + j * 256, ab_hi, bh + j * b_step, ab_hi, idesc, 1u);
+                    mma_tf32(tmem + COL_CROSS, ah + j * 256, ab_hi, bl + j * b_step, ab_hi, idesc, (c == 0 && j == 0) ? 0u : 1u);
+                    mma_tf32(tmem + COL_CROSS, al + j * 256, ab_hi, bh + j * b_step, ab_hi, idesc, 1u);
                     mma_tf32(tmem + COL_MAIN + set, ah + j * 256, ab_hi, bh + j * b_step, ab_hi, idesc, acc);
                 }
                 mma_commit(bar(STAGE_FREE + s));
