@@ -185,8 +185,8 @@ __device__ __forceinline__ void poison_tile(float *out, int row0, int tile, cons
 
 enum { A_FULL = 0, B_FULL = A_FULL + NSTAGES, STAGE_FREE = B_FULL + NSTAGES, ACC_FULL = STAGE_FREE + NSTAGES, ACC_FREE = ACC_FULL + 2, ALL_DONE = ACC_FREE + 2, NBARS };
 
-// 10 warps = 3 per SM sub-partition at most, whose 16,384 registers allow 168 per thread; the register row of the drain
-// (128 floats, touched once per group) is what spills.
+// 10 warps = 3 per SM sub-partition at most, whose 16,384 registers allow 168 per thread: enough for the register row of
+// the drain (128 floats) plus 16 tensor-memory columns in flight.
 // NTM = widest tile the instantiation serves (128 or 256 columns).  The narrow one keeps half the register row, which
 // leaves room for twice as many tensor-memory loads in flight during a fold, and two accumulator sets.
 template <int NTM>
