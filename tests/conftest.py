@@ -9,7 +9,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-UPSTREAM = os.environ.get('QML_LIGHTNING_UPSTREAM', '/root/reference')
+# a checkout of the upstream project, when there is one: QML_LIGHTNING_UPSTREAM, else a `reference` directory beside this repository
+UPSTREAM = os.environ.get('QML_LIGHTNING_UPSTREAM', os.path.join(os.path.dirname(ROOT), 'reference'))
 
 
 def pytest_configure(config):

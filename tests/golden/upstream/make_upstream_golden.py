@@ -36,4 +36,4 @@ def main(upstream):
 
 
 if __name__ == '__main__':
-    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get('QML_LIGHTNING_UPSTREAM', '/root/reference'))
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get('QML_LIGHTNING_UPSTREAM', os.path.join(os.path.dirname(ROOT), 'reference')))
