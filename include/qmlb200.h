@@ -303,7 +303,7 @@ int qmlb_pca_project_jacobian(const float *jac_rows, const float *reductors, con
  * (models/hadamard_features.py:66-80) and build_Z_components (models/kernel.py:134-170), for all elements at once.
  * x f32[rows_cap,N] and dx f32[rows_cap,A,3,N] are element-grouped; Dmat f32[nel,T,S,N], bias f32[nel,S*N] unpacked.
  * Zout f64[nb,F] (overwritten) = per-molecule features; G f64[nb,A,3,F] (overwritten) = -dZ/dr, the force features
- * (dx and G may both be NULL for energy-only training).  sinc_scratch: rows_cap*F floats.  N in [32, 1024]. */
+ * (dx and G may both be NULL for energy-only training).  sinc_scratch: rows_cap*F floats.  N in [32, 512]. */
 int qmlb_sorf_train_features(const float *x, const float *dx, const float *Dmat, const float *bias, const int *group_start,
                              const int *slot_of_row, const int *row_of_slot, const int *atom_counts, int nelements, int nb,
                              int A, size_t rows_cap, int N, int S, int T, float sigma, double *Zout, double *G,

@@ -9,8 +9,8 @@
 //   2. one warp per (molecule, derivative atom j, axis, stack): loops over the centre atoms i of the molecule,
 //      transforms the projected Jacobian row dx[row_i, j, axis, :] and accumulates sinc[row_i] * (HD)^T dx in registers;
 //      every G element is written exactly once (no atomics, no zero-initialisation by the caller).
-// Step 1 uses the warp-shuffle FWHT (N/32 registers per lane), N in [32, 1024].  Step 2, where nearly all the transforms
-// are (atoms x 3 A per atom and stack), uses the register-tile FWHT of the prediction kernel for N <= 512 (16 registers
+// Step 1 uses the warp-shuffle FWHT (N/32 registers per lane), N in [32, 512].  Step 2, where nearly all the transforms
+// are (atoms x 3 A per atom and stack), uses the register-tile FWHT of the prediction kernel (16 registers
 // per lane, one shared-memory transposition instead of five shuffle stages per element) and handles the three axes of a
 // derivative atom in one warp, so that the sin coefficients of a centre atom are read once for the three of them.
 #include <math.h>
@@ -62,58 +62,6 @@ train_features_kernel(const float *__restrict__ x, const float *__restrict__ Dma
         sinc[(size_t)row * F + f] = sn * normf;
     }
 }
-
-template <int E>
-__global__ void __launch_bounds__(256)
-train_derivative_kernel(const float *__restrict__ dx, const float *__restrict__ sinc, const float *__restrict__ Dmat,
-                        const int *__restrict__ row_of_slot, const int *__restrict__ group_start,
-                        const int *__restrict__ atom_counts, int nel, int nb, int A, int S, int T, float scale,
-                        double *__restrict__ G) {
-    constexpr int N = 32 * E;
-    const int lane = threadIdx.x & 31;
-    const long wid = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const long total = (long)nb * A * 3 * S;
-    if (wid >= total) return;
-    const int s = (int)(wid % S);
-    const int xd = (int)((wid / S) % 3);
-    const int j = (int)((wid / ((long)S * 3)) % A);
-    const int mol = (int)(wid / ((long)S * 3 * A));
-    const size_t F = (size_t)S * N;
-    double *dst = G + (((size_t)mol * A + j) * 3 + xd) * F + (size_t)s * N + lane * E;
-    int natoms = atom_counts[mol];
-    natoms = natoms > A ? A : natoms;
-    float acc[E];
-#pragma unroll
-    for (int i = 0; i < E; ++i) acc[i] = 0.f;
-    if (j < natoms) {
-        for (int ia = 0; ia < natoms; ++ia) {
-            const int row = row_of_slot[(size_t)mol * A + ia];
-            if (row < 0) continue;
-            float v[E];
-            const float *src = dx + (((size_t)row * A + j) * 3 + xd) * N + lane * E;
-            bool nz = false;
-#pragma unroll
-            for (int i = 0; i < E; ++i) {
-                v[i] = src[i];
-                nz |= v[i] != 0.f;
-            }
-            if (!__any_sync(QMLB_FULL_MASK, nz)) continue;   // atom j is not a neighbour of atom ia
-            const int el = element_of_row(row, group_start, nel);
-            for (int m = 0; m < T; ++m) {
-                const float *d = Dmat + (((size_t)el * T + m) * S + s) * N + lane * E;
-#pragma unroll
-                for (int i = 0; i < E; ++i) v[i] *= d[i];
-                warp_fwht<E>(v, lane);
-            }
-            const float *sc = sinc + (size_t)row * F + (size_t)s * N + lane * E;
-#pragma unroll
-            for (int i = 0; i < E; ++i) acc[i] = fmaf(sc[i], v[i], acc[i]);
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < E; ++i) dst[i] = (double)(acc[i] * scale);
-}
-
 
 constexpr int TD_WARPS = 4;
 
@@ -280,10 +228,8 @@ int launch_train(const float *x, const float *dx, const float *Dmat, const float
             case 16: return launch_derivative_tile<9>(dx, sinc, Dmat, row_of_slot, group_start, atom_counts, nel, nb, A, S, T, scale, G, st);
             default: break;
         }
-        const long w2 = (long)nb * A * 3 * S;
-        train_derivative_kernel<E><<<(unsigned)((w2 + 7) / 8), 256, 0, st>>>(dx, sinc, Dmat, row_of_slot, group_start,
-                                                                            atom_counts, nel, nb, A, S, T, scale, G);
-        return qmlb::check_launch("qmlb_sorf_train_features(derivative)");
+        qmlb::set_error("qmlb_sorf_train_features: force rows need npcas in [32, 512]");
+        return QMLB_ERR_UNSUPPORTED;
     }
     return QMLB_OK;
 }
@@ -299,7 +245,7 @@ extern "C" int qmlb_sorf_train_features(const float *x, const float *dx, const f
                  "qmlb_sorf_train_features: null tensor");
     QMLB_REQUIRE((dx == nullptr) == (G == nullptr), "qmlb_sorf_train_features: dx and G go together");
     QMLB_REQUIRE(nelements > 0 && nb > 0 && A > 0 && S > 0 && T > 0 && sigma > 0.f, "qmlb_sorf_train_features: bad sizes");
-    QMLB_REQUIRE((long)rows_cap * S / 8 < (1L << 31) && (long)nb * A * 3 * S / 8 < (1L << 31), "qmlb_sorf_train_features: batch too large");
+    QMLB_REQUIRE((long)rows_cap * S / 8 < (1L << 31) && (long)nb * A * S / 4 < (1L << 31), "qmlb_sorf_train_features: batch too large");
     cudaStream_t st = qmlb::as_stream(stream);
     const size_t F = (size_t)S * N;
     if (cudaMemsetAsync(Zout, 0, sizeof(double) * (size_t)nb * F, st) != cudaSuccess)
@@ -314,9 +260,8 @@ extern "C" int qmlb_sorf_train_features(const float *x, const float *dx, const f
         case 128: QMLB_TRAIN(4);
         case 256: QMLB_TRAIN(8);
         case 512: QMLB_TRAIN(16);
-        case 1024: QMLB_TRAIN(32);
         default:
-            qmlb::set_error("qmlb_sorf_train_features: npcas must be a power of two in [32, 1024], got %d", N);
+            qmlb::set_error("qmlb_sorf_train_features: npcas must be a power of two in [32, 512], got %d", N);
             return QMLB_ERR_UNSUPPORTED;
     }
 #undef QMLB_TRAIN
