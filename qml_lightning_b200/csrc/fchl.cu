@@ -317,7 +317,9 @@ fchl_forward_kernel(const float *__restrict__ X, const float *__restrict__ Z, co
         // one broadcast 128-bit load and the lanes cover the radial grid (exp2 with the constant folded in).
         const int ntrip = nn * (nn - 1) / 2;
         float4 *stage = reinterpret_cast<float4 *>(ws + L.off_stage);
-        const float c_exp = -K.eta3 * 1.4426950408889634f;
+        // exp(-eta3 d^2) = 2^-(kk d)^2 with kk = sqrt(eta3 log2 e): the triplet's mean distance and the grid are both
+        // scaled by kk once, so a grid point costs one subtraction, one negated square and the exp2
+        const float kk = sqrtf(K.eta3 * 1.4426950408889634f);
         const bool pair_ok = ((K.nel * K.nRs2) & 1) == 0;   // (cos, sin) columns 8-byte aligned
         for (int t0 = 0; t0 < ntrip; t0 += 32) {
             const int t = t0 + lane;
@@ -328,7 +330,7 @@ fchl_forward_kernel(const float *__restrict__ X, const float *__restrict__ Z, co
                 TripletGeom g;
                 triplet_geometry(ws, A, j, k, K, g);
                 const float amp = ZETA2 * K.w3 * g.T * g.R * g.Fij * g.Fik;
-                tr.x = 0.5f * (g.a + g.b);
+                tr.x = kk * (0.5f * (g.a + g.b));
                 tr.y = amp * g.cth;
                 tr.z = amp * g.sth;
                 tr.w = __int_as_float(pair_block(n_et[j], n_et[k], K));
@@ -337,17 +339,14 @@ fchl_forward_kernel(const float *__restrict__ X, const float *__restrict__ Z, co
             __syncwarp();
             const int cnt = min(32, ntrip - t0);
             if (K.nRs3 <= 32 && pair_ok) {
-                const float rs = lane < K.nRs3 ? sRs3[lane] : 0.f;
+                const float rs = lane < K.nRs3 ? kk * sRs3[lane] : 0.f;
                 for (int q = 0; q < cnt; ++q) {
                     const float4 b = stage[q];
                     if (lane < K.nRs3) {
                         const float d = b.x - rs;
-                        const float radial = ex2_fast(c_exp * d * d);
+                        const float radial = ex2_fast(-d * d);
                         float2 *p2 = reinterpret_cast<float2 *>(acc + __float_as_int(b.w)) + lane;
-                        float2 v = *p2;
-                        v.x = fmaf(radial, b.y, v.x);
-                        v.y = fmaf(radial, b.z, v.y);
-                        *p2 = v;
+                        *p2 = __ffma2_rn(make_float2(radial, radial), make_float2(b.y, b.z), *p2);
                     }
                 }
             } else {
@@ -355,8 +354,8 @@ fchl_forward_kernel(const float *__restrict__ X, const float *__restrict__ Z, co
                     const float4 b = stage[q];
                     const int sidx = __float_as_int(b.w);
                     for (int l = lane; l < K.nRs3; l += 32) {
-                        const float d = b.x - sRs3[l];
-                        const float radial = ex2_fast(c_exp * d * d);
+                        const float d = b.x - kk * sRs3[l];
+                        const float radial = ex2_fast(-d * d);
                         acc[sidx + 2 * l] += radial * b.y;
                         acc[sidx + 2 * l + 1] += radial * b.z;
                     }
@@ -443,7 +442,9 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
         // segmented shuffle reduction and added once by the run's first lane (runs have distinct j, so no atomics);
         // contributions to atom k collide at most between runs and use shared-memory atomics.
         const int ntrip = nn * (nn - 1) / 2;
-        const float c_exp = -K.eta3 * 1.4426950408889634f;
+        // exp(-eta3 d^2) = 2^-(kk d)^2 with kk = sqrt(eta3 log2 e); the loop works on kk d (one fused multiply-add from the
+        // grid point) and the factor 1/kk of the d-weighted sums is applied once per triplet
+        const float kk = sqrtf(K.eta3 * 1.4426950408889634f), inv_kk = 1.0f / kk;
         const bool pair_ok = ((K.nel * K.nRs2) & 1) == 0;   // (cos, sin) gradient columns 8-byte aligned
         for (int t0 = 0; t0 < ntrip; t0 += 32) {
             const int t = t0 + lane;
@@ -459,29 +460,31 @@ fchl_backward_kernel(const float *__restrict__ X, const float *__restrict__ Z, c
                 const float rbar = 0.5f * (g.a + g.b);
                 const float *gb = grow + pair_block(n_et[j], n_et[k], K);
                 float Gc = 0.f, Gs = 0.f, Gcd = 0.f, Gsd = 0.f;   // sums of g radial and of g radial (rbar - Rs3)
+                const float krbar = kk * rbar;
                 if (pair_ok) {
                     const float2 *gb2 = reinterpret_cast<const float2 *>(gb);
+                    float2 G2 = make_float2(0.f, 0.f), Gd2 = make_float2(0.f, 0.f);   // (cos, sin) columns side by side
 #pragma unroll BWD_UNROLL
                     for (int l = 0; l < K.nRs3; ++l) {
-                        const float d = rbar - sRs3[l];
-                        const float radial = ex2_fast(c_exp * d * d);
-                        const float2 gg = gb2[l];
-                        const float gc = gg.x * radial, gs = gg.y * radial;
-                        Gc += gc;
-                        Gs += gs;
-                        Gcd = fmaf(gc, d, Gcd);
-                        Gsd = fmaf(gs, d, Gsd);
+                        const float d = fmaf(-kk, sRs3[l], krbar);
+                        const float radial = ex2_fast(-d * d);
+                        const float2 g2 = __fmul2_rn(gb2[l], make_float2(radial, radial));
+                        G2 = __fadd2_rn(G2, g2);
+                        Gd2 = __ffma2_rn(g2, make_float2(d, d), Gd2);
                     }
+                    Gc = G2.x; Gs = G2.y;
+                    Gcd = Gd2.x * inv_kk; Gsd = Gd2.y * inv_kk;
                 } else {
                     for (int l = 0; l < K.nRs3; ++l) {
-                        const float d = rbar - sRs3[l];
-                        const float radial = ex2_fast(c_exp * d * d);
+                        const float d = fmaf(-kk, sRs3[l], krbar);
+                        const float radial = ex2_fast(-d * d);
                         const float gc = gb[2 * l] * radial, gs = gb[2 * l + 1] * radial;
                         Gc += gc;
                         Gs += gs;
                         Gcd = fmaf(gc, d, Gcd);
                         Gsd = fmaf(gs, d, Gsd);
                     }
+                    Gcd *= inv_kk; Gsd *= inv_kk;
                 }
                 // the amplitudes are constant over the grid: d/d(rbar) of the radial factor, summed first
                 const float Gr = -2.0f * K.eta3 * fmaf(a_cos, Gcd, a_sin * Gsd);
