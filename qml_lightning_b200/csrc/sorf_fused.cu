@@ -349,7 +349,7 @@ struct XposePair {
     }
 };
 
-template <int LOG2N, bool FAST>
+template <int LOG2N, bool FAST, bool SHARE>
 __global__ void __launch_bounds__(WARPS * 32, 4)   // 128 registers, 22 floats spilled: 16 warps per SM beat 12 at 168 registers (12.02 against 12.23 ms on c1)
 sorf_pair_kernel(const float *__restrict__ x, const int *__restrict__ group_start, const int *__restrict__ slot_of_row, int nel,
                  int S, float scale, const float *__restrict__ Dp, const float *__restrict__ bp, const float *__restrict__ ap,
@@ -364,14 +364,20 @@ sorf_pair_kernel(const float *__restrict__ x, const int *__restrict__ group_star
     const int g = lane / C::L, l = lane % C::L;
     float *slab = smem + warp * P::WARP_FLOATS + g * P::SLAB;
 
-    // rows 2k and 2k+1 of an element group (groups are padded to 128 rows) share every parameter load
-    const long row0 = ((long)blockIdx.x * WARPS + warp) * 2;
-    if (row0 >= group_start[nel]) return;
+    // Rows 2k and 2k+1 of an element group share the registers of a lane.  SHARE: the V lane groups of the warp take V such
+    // pairs and walk the stacks together, so that a parameter load is one request for all 2 V atoms (lanes of different
+    // groups read the same addresses); used when there are rows enough to fill the GPU that way.  Otherwise the V lane
+    // groups take V consecutive stacks of the same pair and their partial sums are added at the end (V times as many
+    // warps, each V times shorter: small batches).  Groups are padded to 128 rows, so a warp's rows belong to one element.
+    constexpr int RPW = SHARE ? 2 * C::V : 2;
+    const long rowb = ((long)blockIdx.x * WARPS + warp) * RPW;
+    if (rowb >= group_start[nel]) return;
     int el = 0;
-    while (el + 1 < nel && row0 >= group_start[el + 1]) ++el;
+    while (el + 1 < nel && rowb >= group_start[el + 1]) ++el;
+    const long row0 = rowb + (SHARE ? 2 * g : 0);
     const bool live0 = slot_of_row[row0] >= 0, live1 = slot_of_row[row0 + 1] >= 0;
-    if (!live0 && !live1) {
-        if (lane == 0) atom_energy[row0] = atom_energy[row0 + 1] = 0.f;
+    if (!__any_sync(QMLB_FULL_MASK, live0 || live1)) {     // padding only
+        if (l == 0 && (SHARE || g == 0)) atom_energy[row0] = atom_energy[row0 + 1] = 0.f;
         return;
     }
     float2 xr[16], gx[16];
@@ -391,8 +397,8 @@ sorf_pair_kernel(const float *__restrict__ x, const int *__restrict__ group_star
     const float *bp_e = bp + (size_t)el * S * N;
     const float2 scale2 = make_float2(scale, scale);
 
-    for (int s0 = 0; s0 < S; s0 += C::V) {
-        const int sc = s0 + g;
+    for (int s0 = 0; s0 < S; s0 += SHARE ? 1 : C::V) {
+        const int sc = SHARE ? s0 : s0 + g;
         float c[16];
         float2 u[16];
         load16<C::L>(c, Dp_e + (size_t)sc * N + pos);
@@ -432,16 +438,23 @@ sorf_pair_kernel(const float *__restrict__ x, const int *__restrict__ group_star
         for (int e = 0; e < 16; ++e) gx[e] = __ffma2_rn(u[e], make_float2(c[e], c[e]), gx[e]);
     }
 
-    // sum the V stacks processed side by side, then one store per atom; grad = -scale * sum (alpha sin ...) (HD)^T
+    // energies: sum over the lanes that hold the pair; grad = -scale * sum (alpha sin ...) (HD)^T
+    if (!SHARE) {   // the V stacks processed side by side
 #pragma unroll
-    for (int off = C::L; off < 32; off <<= 1)
+        for (int off = C::L; off < 32; off <<= 1)
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-            gx[e].x += __shfl_xor_sync(QMLB_FULL_MASK, gx[e].x, off);
-            gx[e].y += __shfl_xor_sync(QMLB_FULL_MASK, gx[e].y, off);
-        }
-    const float e0 = warp_sum(eacc.x), e1 = warp_sum(eacc.y);
-    if (g == 0) {
+            for (int e = 0; e < 16; ++e) {
+                gx[e].x += __shfl_xor_sync(QMLB_FULL_MASK, gx[e].x, off);
+                gx[e].y += __shfl_xor_sync(QMLB_FULL_MASK, gx[e].y, off);
+            }
+    }
+    float e0 = eacc.x, e1 = eacc.y;
+#pragma unroll
+    for (int off = (SHARE ? C::L : 32) / 2; off > 0; off >>= 1) {
+        e0 += __shfl_xor_sync(QMLB_FULL_MASK, e0, off);
+        e1 += __shfl_xor_sync(QMLB_FULL_MASK, e1, off);
+    }
+    if (SHARE || g == 0) {
         const float ns = -scale;
         if (live0) {
             float4 *dst = reinterpret_cast<float4 *>(grad_x + (size_t)row0 * N + l * 16);
@@ -456,7 +469,7 @@ sorf_pair_kernel(const float *__restrict__ x, const int *__restrict__ group_star
                 dst[q] = make_float4(gx[4 * q].y * ns, gx[4 * q + 1].y * ns, gx[4 * q + 2].y * ns, gx[4 * q + 3].y * ns);
         }
     }
-    if (lane == 0) {
+    if (l == 0 && (SHARE || g == 0)) {
         atom_energy[row0] = live0 ? e0 : 0.f;
         atom_energy[row0 + 1] = live1 ? e1 : 0.f;
     }
@@ -537,9 +550,15 @@ int launch_fused(const float *x, const int *group_start, const int *slot_of_row,
     if (T == 1 && LOG2N >= 6 && LOG2N <= 8 && SORF_PAIR) {
         constexpr int PL = (LOG2N >= 6 && LOG2N <= 8) ? LOG2N : 8;   // keeps the other instantiations well formed
         const size_t smem = sizeof(float) * WARPS * PairCfg<PL>::WARP_FLOATS;
-        const unsigned grid = (unsigned)((rows_cap + WARPS * 2 - 1) / (WARPS * 2));
-        if (fast) sorf_pair_kernel<PL, true><<<grid, WARPS * 32, smem, st>>>(x, group_start, slot_of_row, nel, S, scale, Dp, bp, ap, atom_energy, grad_x);
-        else sorf_pair_kernel<PL, false><<<grid, WARPS * 32, smem, st>>>(x, group_start, slot_of_row, nel, S, scale, Dp, bp, ap, atom_energy, grad_x);
+        // one warp per 2 V rows when that still gives every SM several waves of warps, else one warp per 2 rows
+        const bool share = rows_cap / (2 * Cfg<PL>::V) >= (size_t)148 * 16 * 4;
+        const int rpw = share ? 2 * Cfg<PL>::V : 2;
+        const unsigned grid = (unsigned)((rows_cap + WARPS * rpw - 1) / (WARPS * rpw));
+#define QMLB_PAIR(FASTV, SHAREV) \
+    sorf_pair_kernel<PL, FASTV, SHAREV><<<grid, WARPS * 32, smem, st>>>(x, group_start, slot_of_row, nel, S, scale, Dp, bp, ap, atom_energy, grad_x)
+        if (fast) { if (share) QMLB_PAIR(true, true); else QMLB_PAIR(true, false); }
+        else { if (share) QMLB_PAIR(false, true); else QMLB_PAIR(false, false); }
+#undef QMLB_PAIR
     } else if (T == 1) {
         if (fast) QMLB_LAUNCH(true, 1, ATOMS_FAST); else QMLB_LAUNCH(false, 1, 1);
     } else {
