@@ -11,6 +11,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "sincos.cuh"
 
 namespace {
 
@@ -102,7 +103,7 @@ rff_energy_grad_kernel(const float *__restrict__ x, const int *__restrict__ grou
             for (int i = 0; i < 4; ++i) {
                 float sn, cs;
                 if (FAST) __sincosf(acc[i][c] + bf, &sn, &cs);
-                else sincosf(acc[i][c] + bf, &sn, &cs);
+                else qmlb_sincos::sincos_one(acc[i][c] + bf, sn, cs);
                 eacc[i] = fmaf(af, cs, eacc[i]);
                 g[i] = -af * sn;
             }

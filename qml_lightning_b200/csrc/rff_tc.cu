@@ -53,6 +53,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "sincos.cuh"
 
 namespace {
 
@@ -482,7 +483,7 @@ rff_tc_kernel(const float *__restrict__ x, const int *__restrict__ group_start, 
                     const float a = fmaf(__uint_as_float(av[f]) + __uint_as_float(cv[f]), arg_scale, prm[f]);
                     float sn, cs;
                     if (FAST) __sincosf(a, &sn, &cs);
-                    else sincosf(a, &sn, &cs);
+                    else qmlb_sincos::sincos_one(a, sn, cs);
                     echunk = fmaf(prm[FC + f], cs, echunk);
                     gq[t] = prm[2 * FC + f] * sn;
                 }
